@@ -1,0 +1,193 @@
+"""B200 (sm_100a) tensor-core GEMM: Python front end of the C ABI.
+
+The product is ``libckl_gemm.so`` (hand-written CUDA, C ABI declared in
+``include/ckl_gemm.h``).  This module only binds it with ctypes and mirrors
+the reference library's entry points (``include/ckl/gemm.hpp:68-100`` there):
+same names, same argument order and meaning, row-major device pointers,
+``stream`` last, an exception where the C++ launchers throw.
+
+Pointers may be given as integers or as anything with ``data_ptr()`` (a torch
+tensor is only a convenient owner of device memory; nothing here computes with
+torch).  There is no CPU path: without the compiled library the import fails,
+and without an sm_100 GPU every call raises ``CklError``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libckl_gemm.so")
+
+# ckl_status
+OK, ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE, ERR_TOO_LARGE = range(6)
+# ckl_dtype
+F32, F16, BF16 = 0, 1, 2
+# ckl_algo
+ALGO_AUTO, ALGO_SIMT, ALGO_UMMA_1CTA, ALGO_UMMA_SK, ALGO_UMMA_2CTA, ALGO_UMMA_2CTA_SK = range(6)
+
+
+class CklError(RuntimeError):
+    """A non-zero ckl_status; ``status`` holds the code, the text is ckl_last_error()."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"ckl status {status}: {message}")
+        self.status = status
+
+
+class Plan(ctypes.Structure):
+    _fields_ = [
+        ("algo", ctypes.c_int), ("tile_m", ctypes.c_int), ("tile_n", ctypes.c_int),
+        ("tile_k", ctypes.c_int), ("tiles_m", ctypes.c_int), ("tiles_n", ctypes.c_int),
+        ("k_blocks", ctypes.c_int), ("grid", ctypes.c_int), ("dp_tiles", ctypes.c_int),
+        ("sk_tiles", ctypes.c_int), ("sk_units", ctypes.c_int), ("sk_iters", ctypes.c_longlong),
+        ("workspace_bytes", ctypes.c_size_t),
+    ]
+
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python {os.path.join(_HERE, 'build.py')}` "
+        "(needs nvcc; there is no fallback implementation)")
+
+_lib = ctypes.CDLL(LIB_PATH)
+
+_vp, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+_lib.ckl_gemm_f16.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]
+_lib.ckl_gemm_bf16.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]
+_lib.ckl_gemm_ex.argtypes = [_i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i, _vp]
+_lib.ckl_gemm_bias_relu_ex.argtypes = [_i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _i,
+                                       _vp]
+_lib.ckl_bias_relu_f32.argtypes = [_vp, _vp, _i, _i, _i, _vp]
+_lib.ckl_gemm_host.argtypes = [_i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f]
+_lib.ckl_plan_gemm.argtypes = [_i, _i, _i, _i, _i, _i, _i, _i, _i, _i, ctypes.POINTER(Plan)]
+_lib.ckl_plan_sk_range.argtypes = [ctypes.POINTER(Plan), _i, ctypes.POINTER(ctypes.c_longlong),
+                                   ctypes.POINTER(ctypes.c_longlong)]
+_lib.ckl_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
+_lib.ckl_stream_copy.argtypes = [_vp, _vp, ctypes.c_size_t, _vp]
+_lib.ckl_last_error.restype = ctypes.c_char_p
+_lib.ckl_algo_name.argtypes = [_i]
+_lib.ckl_algo_name.restype = ctypes.c_char_p
+_lib.ckl_shutdown.restype = None
+for _name in ("ckl_gemm_f16", "ckl_gemm_bf16", "ckl_gemm_ex", "ckl_gemm_bias_relu_ex",
+              "ckl_bias_relu_f32", "ckl_gemm_host", "ckl_plan_gemm", "ckl_plan_sk_range",
+              "ckl_device_status", "ckl_stream_copy"):
+    getattr(_lib, _name).restype = ctypes.c_int
+
+
+def _ptr(x) -> int | None:
+    if x is None:
+        return None
+    if hasattr(x, "data_ptr"):
+        return int(x.data_ptr())
+    return int(x)
+
+
+def _stream(s) -> int | None:
+    if s is None:
+        return None
+    if hasattr(s, "cuda_stream"):
+        return int(s.cuda_stream)
+    return int(s)
+
+
+def _check(status: int) -> None:
+    if status != OK:
+        raise CklError(status, _lib.ckl_last_error().decode())
+
+
+def last_error() -> str:
+    return _lib.ckl_last_error().decode()
+
+
+def algo_name(algo: int) -> str:
+    return _lib.ckl_algo_name(algo).decode()
+
+
+def gemm_ex(ab_dtype, a, b, c, c_dtype, m, n, k, lda, ldb, ldc, alpha, beta, algo=ALGO_AUTO,
+            stream=None) -> None:
+    """C = alpha*A*B + beta*C with explicit dtypes, leading dimensions and kernel choice."""
+    _check(_lib.ckl_gemm_ex(ab_dtype, _ptr(a), _ptr(b), _ptr(c), c_dtype, m, n, k, lda, ldb, ldc,
+                            alpha, beta, algo, _stream(stream)))
+
+
+def gemm_f16(a, b, c, c_dtype, m, n, k, lda, ldb, ldc, alpha, beta, stream=None) -> None:
+    _check(_lib.ckl_gemm_f16(_ptr(a), _ptr(b), _ptr(c), c_dtype, m, n, k, lda, ldb, ldc, alpha,
+                             beta, _stream(stream)))
+
+
+def gemm_bf16(a, b, c, c_dtype, m, n, k, lda, ldb, ldc, alpha, beta, stream=None) -> None:
+    _check(_lib.ckl_gemm_bf16(_ptr(a), _ptr(b), _ptr(c), c_dtype, m, n, k, lda, ldb, ldc, alpha,
+                              beta, _stream(stream)))
+
+
+# --- the reference's entry points, FP32 C, lda = k, ldb = ldc = n ---------------------
+# (include/ckl/gemm.hpp:68-86 of the reference; every FP16 rung is the same function.)
+
+def gemm_wmma_fp16(a, b, c, m, n, k, alpha, beta, stream=None) -> None:
+    gemm_f16(a, b, c, F32, m, n, k, k, n, n, alpha, beta, stream)
+
+
+def gemm_wmma_bf16(a, b, c, m, n, k, alpha, beta, stream=None) -> None:
+    gemm_bf16(a, b, c, F32, m, n, k, k, n, n, alpha, beta, stream)
+
+
+gemm_mma_ptx = gemm_wmma_fp16
+gemm_mma_ldm = gemm_wmma_fp16
+gemm_mma_opt = gemm_wmma_fp16
+
+
+def gemm_mma_opt_bias(a, b, c, bias, m, n, k, alpha, stream=None) -> None:
+    """C = relu(alpha*A*B + bias[col]); include/ckl/gemm.hpp:91-92 of the reference."""
+    _check(_lib.ckl_gemm_bias_relu_ex(F16, _ptr(a), _ptr(b), _ptr(c), F32, _ptr(bias), m, n, k, k,
+                                      n, n, alpha, ALGO_AUTO, _stream(stream)))
+
+
+def gemm_bias_relu_ex(ab_dtype, a, b, c, c_dtype, bias, m, n, k, lda, ldb, ldc, alpha,
+                      algo=ALGO_AUTO, stream=None) -> None:
+    _check(_lib.ckl_gemm_bias_relu_ex(ab_dtype, _ptr(a), _ptr(b), _ptr(c), c_dtype, _ptr(bias), m,
+                                      n, k, lda, ldb, ldc, alpha, algo, _stream(stream)))
+
+
+def gemm_bias_relu(c, bias, m, n, stream=None) -> None:
+    """Unfused pass C = relu(C + bias[col]); include/ckl/gemm.hpp:93 of the reference."""
+    _check(_lib.ckl_bias_relu_f32(_ptr(c), _ptr(bias), m, n, n, _stream(stream)))
+
+
+def gemm_host(ab_dtype, a_host, b_host, c_host, c_dtype, m, n, k, alpha, beta) -> None:
+    """Whole call on HOST buffers (upload, GEMM, download, wait)."""
+    _check(_lib.ckl_gemm_host(ab_dtype, _ptr(a_host), _ptr(b_host), _ptr(c_host), c_dtype, m, n, k,
+                              alpha, beta))
+
+
+def plan_gemm(m, n, k, lda=None, ldb=None, ldc=None, a_align=16, b_align=16, algo=ALGO_AUTO,
+              sm_count=148) -> Plan:
+    """What a call would launch on a device with ``sm_count`` SMs.  Pure host arithmetic."""
+    plan = Plan()
+    _check(_lib.ckl_plan_gemm(m, n, k, k if lda is None else lda, n if ldb is None else ldb,
+                              n if ldc is None else ldc, a_align, b_align, algo, sm_count,
+                              ctypes.byref(plan)))
+    return plan
+
+
+def plan_sk_range(plan: Plan, unit: int) -> tuple[int, int]:
+    b, e = ctypes.c_longlong(), ctypes.c_longlong()
+    _check(_lib.ckl_plan_sk_range(ctypes.byref(plan), unit, ctypes.byref(b), ctypes.byref(e)))
+    return b.value, e.value
+
+
+def device_status() -> list[int]:
+    """Synchronise and read the device health word; raises CklError(ERR_DEVICE) if a
+    kernel gave up a bounded wait."""
+    info = (ctypes.c_uint * 4)()
+    _check(_lib.ckl_device_status(info))
+    return list(info)
+
+
+def stream_copy(dst, src, nbytes: int, stream=None) -> None:
+    _check(_lib.ckl_stream_copy(_ptr(dst), _ptr(src), nbytes, _stream(stream)))
+
+
+def shutdown() -> None:
+    _lib.ckl_shutdown()

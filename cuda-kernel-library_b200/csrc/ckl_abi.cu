@@ -1,0 +1,724 @@
+// C ABI of the library (include/ckl_gemm.h): argument checking, the planner
+// that picks a kernel and a tile schedule, TMA descriptor construction, the
+// per-device state (status word, stream-K workspace, host staging buffers) and
+// the launches.  Only the CUDA runtime is linked; the one driver entry point
+// needed (cuTensorMapEncodeTiled) is fetched through the runtime.
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "ckl_gemm.h"
+#include "gemm_simt.cuh"
+#include "gemm_umma.cuh"
+#include "tile_sched.h"
+
+namespace {
+
+using namespace ckl;
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+#define CKL_TRY_CUDA(expr)                                                                  \
+    do {                                                                                    \
+        const cudaError_t err__ = (expr);                                                   \
+        if (err__ != cudaSuccess) {                                                         \
+            return fail(CKL_ERR_CUDA, "%s failed: %s (%s)", #expr, cudaGetErrorName(err__), \
+                        cudaGetErrorString(err__));                                         \
+        }                                                                                   \
+    } while (0)
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct Staging {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+};
+
+struct DeviceCtx {
+    int device = -1;
+    int sm_count = 0;
+    int cc_major = 0;
+    int max_pairs = 0;
+    EncodeTiledFn encode = nullptr;
+    unsigned int* status = nullptr;            // 4 words on the device
+    std::map<cudaStream_t, Staging> workspace; // stream-K partial slots, one per stream
+    Staging host_a, host_b, host_c;            // device staging for ckl_gemm_host
+    cudaStream_t host_stream = nullptr;
+    bool attrs_set = false;
+    std::mutex mu;
+};
+
+std::mutex g_ctx_mu;
+std::map<int, std::unique_ptr<DeviceCtx>> g_ctx;
+
+template <bool kPair, typename OutT>
+cudaError_t set_umma_attr() {
+    return cudaFuncSetAttribute(umma_gemm_kernel<kPair, OutT>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                static_cast<int>(UmmaConfig<kPair>::kSmemBytes));
+}
+
+int get_ctx(DeviceCtx** out) {
+    int dev = 0;
+    CKL_TRY_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_ctx_mu);
+    auto it = g_ctx.find(dev);
+    if (it != g_ctx.end()) {
+        *out = it->second.get();
+        return CKL_OK;
+    }
+    auto ctx = std::make_unique<DeviceCtx>();
+    ctx->device = dev;
+    cudaDeviceProp prop;
+    CKL_TRY_CUDA(cudaGetDeviceProperties(&prop, dev));
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->cc_major = prop.major;
+    if (prop.major != 10) {
+        return fail(CKL_ERR_UNSUPPORTED,
+                    "device %d is compute capability %d.%d; this library is built for sm_100a only",
+                    dev, prop.major, prop.minor);
+    }
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    CKL_TRY_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (fn == nullptr || qres != cudaDriverEntryPointSuccess) {
+        return fail(CKL_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    }
+    ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
+    CKL_TRY_CUDA(cudaMalloc(&ctx->status, 4 * sizeof(unsigned int)));
+    CKL_TRY_CUDA(cudaMemset(ctx->status, 0, 4 * sizeof(unsigned int)));
+    CKL_TRY_CUDA((set_umma_attr<false, float>()));
+    CKL_TRY_CUDA((set_umma_attr<false, __half>()));
+    CKL_TRY_CUDA((set_umma_attr<false, __nv_bfloat16>()));
+    CKL_TRY_CUDA((set_umma_attr<true, float>()));
+    CKL_TRY_CUDA((set_umma_attr<true, __half>()));
+    CKL_TRY_CUDA((set_umma_attr<true, __nv_bfloat16>()));
+    // How many CTA pairs can be resident at once (pairs must share a TPC/GPC).
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(ctx->sm_count / 2 * 2));
+        cfg.blockDim = dim3(UmmaConfig<true>::kThreads);
+        cfg.dynamicSmemBytes = UmmaConfig<true>::kSmemBytes;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        const cudaError_t e =
+            cudaOccupancyMaxActiveClusters(&clusters, umma_gemm_kernel<true, float>, &cfg);
+        if (e != cudaSuccess || clusters <= 0) {
+            (void)cudaGetLastError();
+            clusters = ctx->sm_count / 2;
+        }
+        ctx->max_pairs = std::min(clusters, ctx->sm_count / 2);
+    }
+    *out = ctx.get();
+    g_ctx[dev] = std::move(ctx);
+    return CKL_OK;
+}
+
+size_t dtype_size(int dtype) { return dtype == CKL_F32 ? 4 : 2; }
+
+bool is_tensor_algo(int algo) { return algo >= CKL_ALGO_UMMA_1CTA && algo <= CKL_ALGO_UMMA_2CTA_SK; }
+bool is_pair_algo(int algo) { return algo == CKL_ALGO_UMMA_2CTA || algo == CKL_ALGO_UMMA_2CTA_SK; }
+
+// ---- planner (pure host arithmetic) ------------------------------------------
+
+struct Plan {
+    int algo = CKL_ALGO_SIMT;
+    bool pair = false;
+    int tile_m = 64, tile_n = 64, tile_k = 16;
+    int grid = 0;
+    Schedule sched = {};
+    size_t workspace_bytes = 0;
+};
+
+bool tma_legal(int k, int lda, int ldb, size_t a_align, size_t b_align) {
+    return k > 0 && lda % 8 == 0 && ldb % 8 == 0 && a_align % 16 == 0 && b_align % 16 == 0;
+}
+
+// want_sk: 0 = never, 1 = always when a remainder exists, 2 = heuristic.
+Schedule make_schedule(int m, int n, int k, bool pair, int max_units, int want_sk) {
+    Schedule s = {};
+    const int tile_m = pair ? 256 : 128;
+    s.tiles_m = (m + tile_m - 1) / tile_m;
+    s.tiles_n = (n + 255) / 256;
+    s.k_blocks = (k + 63) / 64;
+    s.group_m = pair ? 8 : 16;
+    const int tiles = s.tiles_m * s.tiles_n;
+    s.units = std::max(1, std::min(max_units, tiles));
+    s.dp_tiles = tiles;
+    s.sk_tiles = 0;
+    s.sk_iters = 0;
+    if (want_sk == 0 || max_units <= 0) {
+        return s;
+    }
+    const int full_waves = tiles / max_units;
+    const int rem = tiles % max_units;
+    if (rem == 0) {
+        return s;
+    }
+    int sk_tiles = rem;
+    // Give every unit a few k blocks of split work: if the remainder alone is
+    // too thin, fold one full wave into the split region as well.
+    if (full_waves >= 1 && static_cast<long long>(rem) * s.k_blocks < 4LL * max_units) {
+        sk_tiles = rem + max_units;
+    }
+    const long long sk_iters = static_cast<long long>(sk_tiles) * s.k_blocks;
+    if (want_sk == 2) {
+        // Heuristic: split only when the last data-parallel wave would leave a
+        // noticeable part of the machine idle and the split ranges are long
+        // enough to amortise the partial-tile traffic.
+        const int waves = full_waves + 1;
+        const double dp_eff = static_cast<double>(tiles) / (static_cast<double>(waves) * max_units);
+        if (dp_eff > 0.97 || sk_iters / max_units < 8) {
+            return s;
+        }
+    }
+    if (sk_iters < max_units) {
+        return s;  // fewer k blocks than units: nothing to balance
+    }
+    s.units = max_units;
+    s.sk_tiles = sk_tiles;
+    s.dp_tiles = tiles - sk_tiles;
+    s.sk_iters = sk_iters;
+    return s;
+}
+
+int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_align, int algo,
+              int sm_count, int max_pairs, Plan* plan) {
+    const bool legal = tma_legal(k, lda, ldb, a_align, b_align);
+    int resolved = algo;
+    if (algo == CKL_ALGO_AUTO) {
+        resolved = legal ? CKL_ALGO_UMMA_SK : CKL_ALGO_SIMT;
+    } else if (is_tensor_algo(algo) && !legal) {
+        return fail(CKL_ERR_UNSUPPORTED,
+                    "tensor-core algo %s needs k > 0, A and B 16-byte aligned and lda, ldb "
+                    "multiples of 8 elements (lda=%d ldb=%d k=%d)",
+                    ckl_algo_name(algo), lda, ldb, k);
+    } else if (algo < CKL_ALGO_AUTO || algo > CKL_ALGO_UMMA_2CTA_SK) {
+        return fail(CKL_ERR_INVALID_ARG, "unknown algo %d", algo);
+    }
+    plan->algo = resolved;
+    if (resolved == CKL_ALGO_SIMT) {
+        plan->pair = false;
+        plan->tile_m = 64;
+        plan->tile_n = 64;
+        plan->tile_k = 16;
+        plan->sched = {};
+        plan->sched.tiles_m = (m + 63) / 64;
+        plan->sched.tiles_n = (n + 63) / 64;
+        plan->sched.k_blocks = (k + 15) / 16;
+        plan->sched.dp_tiles = plan->sched.tiles_m * plan->sched.tiles_n;
+        plan->sched.units = plan->sched.dp_tiles;
+        plan->grid = plan->sched.dp_tiles;
+        plan->workspace_bytes = 0;
+        return CKL_OK;
+    }
+    const bool pair = is_pair_algo(resolved);
+    int want_sk = 0;
+    if (resolved == CKL_ALGO_UMMA_SK || resolved == CKL_ALGO_UMMA_2CTA_SK) {
+        want_sk = (algo == CKL_ALGO_AUTO) ? 2 : 1;
+    }
+    const int max_units = pair ? max_pairs : sm_count;
+    if (max_units <= 0) {
+        return fail(CKL_ERR_UNSUPPORTED, "no schedulable units (sm_count=%d)", sm_count);
+    }
+    plan->pair = pair;
+    plan->tile_m = pair ? 256 : 128;
+    plan->tile_n = 256;
+    plan->tile_k = 64;
+    plan->sched = make_schedule(m, n, k, pair, max_units, want_sk);
+    plan->grid = plan->sched.units * (pair ? 2 : 1);
+    if (plan->sched.sk_tiles > 0) {
+        const size_t slot = (pair ? UmmaConfig<true>::kSlotFloats : UmmaConfig<false>::kSlotFloats) *
+                            sizeof(float);
+        plan->workspace_bytes = 2ull * static_cast<size_t>(plan->sched.units) * slot;
+    } else {
+        plan->workspace_bytes = 0;
+        if (algo == CKL_ALGO_AUTO) {
+            plan->algo = CKL_ALGO_UMMA_1CTA;
+        }
+    }
+    return CKL_OK;
+}
+
+// ---- TMA descriptors -----------------------------------------------------------
+
+int encode_2d(DeviceCtx* ctx, CUtensorMap* map, int ab_dtype, const void* base, uint64_t inner,
+              uint64_t outer, uint64_t pitch_elems, uint32_t box_inner, uint32_t box_outer) {
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {pitch_elems * 2ull};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUtensorMapDataType dt =
+        ab_dtype == CKL_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const CUresult r = ctx->encode(map, dt, 2, const_cast<void*>(base), dims, strides, box,
+                                   elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        return fail(CKL_ERR_CUDA,
+                    "cuTensorMapEncodeTiled failed with CUresult %d (base=%p dims=%llu x %llu "
+                    "pitch=%llu box=%u x %u)",
+                    static_cast<int>(r), base, static_cast<unsigned long long>(inner),
+                    static_cast<unsigned long long>(outer),
+                    static_cast<unsigned long long>(pitch_elems), box_inner, box_outer);
+    }
+    return CKL_OK;
+}
+
+int get_workspace(DeviceCtx* ctx, cudaStream_t stream, size_t bytes, float** out) {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    Staging& w = ctx->workspace[stream];
+    if (w.bytes < bytes) {
+        if (w.ptr != nullptr) {
+            CKL_TRY_CUDA(cudaStreamSynchronize(stream));
+            CKL_TRY_CUDA(cudaFree(w.ptr));
+            w.ptr = nullptr;
+            w.bytes = 0;
+        }
+        CKL_TRY_CUDA(cudaMalloc(&w.ptr, bytes));
+        w.bytes = bytes;
+    }
+    *out = static_cast<float*>(w.ptr);
+    return CKL_OK;
+}
+
+// ---- launches --------------------------------------------------------------------
+
+template <bool kPair, typename OutT>
+int launch_umma(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+                cudaStream_t stream) {
+    using Cfg = UmmaConfig<kPair>;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(Cfg::kThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    if (kPair) {
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+    }
+    CKL_TRY_CUDA(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<kPair, OutT>, ta, tb, p));
+    if (p.sched.sk_tiles > 0) {
+        streamk_fixup_kernel<Cfg::kTileM, OutT><<<p.sched.sk_tiles, 256, 0, stream>>>(p);
+        CKL_TRY_CUDA(cudaGetLastError());
+    }
+    return CKL_OK;
+}
+
+template <typename OutT>
+int launch_umma_out(bool pair, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                    int grid, cudaStream_t stream) {
+    return pair ? launch_umma<true, OutT>(ta, tb, p, grid, stream)
+                : launch_umma<false, OutT>(ta, tb, p, grid, stream);
+}
+
+template <typename InT, typename OutT>
+int launch_simt(const void* a, const void* b, void* c, const float* bias, int m, int n, int k,
+                int lda, int ldb, int ldc, float alpha, float beta, int epi, cudaStream_t stream) {
+    const dim3 grid(static_cast<unsigned>((n + 63) / 64), static_cast<unsigned>((m + 63) / 64));
+    simt_gemm_kernel<InT, OutT><<<grid, 256, 0, stream>>>(
+        static_cast<const InT*>(a), static_cast<const InT*>(b), static_cast<OutT*>(c), bias, m, n, k,
+        lda, ldb, ldc, alpha, beta, epi);
+    CKL_TRY_CUDA(cudaGetLastError());
+    return CKL_OK;
+}
+
+template <typename InT>
+int launch_simt_in(int c_dtype, const void* a, const void* b, void* c, const float* bias, int m,
+                   int n, int k, int lda, int ldb, int ldc, float alpha, float beta, int epi,
+                   cudaStream_t stream) {
+    switch (c_dtype) {
+        case CKL_F32:
+            return launch_simt<InT, float>(a, b, c, bias, m, n, k, lda, ldb, ldc, alpha, beta, epi,
+                                           stream);
+        case CKL_F16:
+            return launch_simt<InT, __half>(a, b, c, bias, m, n, k, lda, ldb, ldc, alpha, beta, epi,
+                                            stream);
+        default:
+            return launch_simt<InT, __nv_bfloat16>(a, b, c, bias, m, n, k, lda, ldb, ldc, alpha,
+                                                   beta, epi, stream);
+    }
+}
+
+template <typename OutT>
+int launch_scale(void* c, const float* bias, int m, int n, int ldc, float beta, int epi,
+                 cudaStream_t stream) {
+    const long long total = static_cast<long long>(m) * n;
+    const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148LL * 16));
+    scale_c_kernel<OutT><<<blocks, 256, 0, stream>>>(static_cast<OutT*>(c), bias, m, n, ldc, beta,
+                                                     epi);
+    CKL_TRY_CUDA(cudaGetLastError());
+    return CKL_OK;
+}
+
+int gemm_impl(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, const float* bias,
+              int m, int n, int k, int lda, int ldb, int ldc, float alpha, float beta, int epi,
+              int algo, cudaStream_t stream) {
+    if (ab_dtype != CKL_F16 && ab_dtype != CKL_BF16) {
+        return fail(CKL_ERR_INVALID_ARG, "A/B dtype must be CKL_F16 or CKL_BF16 (got %d)", ab_dtype);
+    }
+    if (c_dtype != CKL_F32 && c_dtype != CKL_F16 && c_dtype != CKL_BF16) {
+        return fail(CKL_ERR_INVALID_ARG, "C dtype must be CKL_F32, CKL_F16 or CKL_BF16 (got %d)",
+                    c_dtype);
+    }
+    if (algo < CKL_ALGO_AUTO || algo > CKL_ALGO_UMMA_2CTA_SK) {
+        return fail(CKL_ERR_INVALID_ARG, "unknown algo %d", algo);
+    }
+    if (m <= 0 || n <= 0) {
+        return CKL_OK;  // nothing to write (reference: wmma_gemm.cuh:145-147)
+    }
+    if (c == nullptr) {
+        return fail(CKL_ERR_INVALID_ARG, "C is null");
+    }
+    if (ldc < n) {
+        return fail(CKL_ERR_INVALID_ARG, "ldc=%d is smaller than n=%d", ldc, n);
+    }
+    if (epi == kEpiBiasRelu && bias == nullptr) {
+        return fail(CKL_ERR_INVALID_ARG, "bias is null");
+    }
+    DeviceCtx* ctx = nullptr;
+    if (const int rc = get_ctx(&ctx); rc != CKL_OK) {
+        return rc;
+    }
+    if (k <= 0) {
+        switch (c_dtype) {
+            case CKL_F32: return launch_scale<float>(c, bias, m, n, ldc, beta, epi, stream);
+            case CKL_F16: return launch_scale<__half>(c, bias, m, n, ldc, beta, epi, stream);
+            default: return launch_scale<__nv_bfloat16>(c, bias, m, n, ldc, beta, epi, stream);
+        }
+    }
+    if (a == nullptr || b == nullptr) {
+        return fail(CKL_ERR_INVALID_ARG, "A or B is null");
+    }
+    if (lda < k || ldb < n) {
+        return fail(CKL_ERR_INVALID_ARG, "lda=%d < k=%d or ldb=%d < n=%d", lda, k, ldb, n);
+    }
+    Plan plan;
+    const size_t a_align = reinterpret_cast<uintptr_t>(a) % 16 == 0 ? 16 : 2;
+    const size_t b_align = reinterpret_cast<uintptr_t>(b) % 16 == 0 ? 16 : 2;
+    if (const int rc = make_plan(m, n, k, lda, ldb, a_align, b_align, algo, ctx->sm_count,
+                                 ctx->max_pairs, &plan);
+        rc != CKL_OK) {
+        return rc;
+    }
+    if (plan.algo == CKL_ALGO_SIMT) {
+        return ab_dtype == CKL_F16
+                   ? launch_simt_in<__half>(c_dtype, a, b, c, bias, m, n, k, lda, ldb, ldc, alpha,
+                                            beta, epi, stream)
+                   : launch_simt_in<__nv_bfloat16>(c_dtype, a, b, c, bias, m, n, k, lda, ldb, ldc,
+                                                   alpha, beta, epi, stream);
+    }
+
+    CUtensorMap ta, tb;
+    if (const int rc = encode_2d(ctx, &ta, ab_dtype, a, static_cast<uint64_t>(k),
+                                 static_cast<uint64_t>(m), static_cast<uint64_t>(lda), 64, 128);
+        rc != CKL_OK) {
+        return rc;
+    }
+    if (const int rc = encode_2d(ctx, &tb, ab_dtype, b, static_cast<uint64_t>(n),
+                                 static_cast<uint64_t>(k), static_cast<uint64_t>(ldb), 64, 64);
+        rc != CKL_OK) {
+        return rc;
+    }
+    GemmParams p = {};
+    p.c = c;
+    p.bias = bias;
+    p.workspace = nullptr;
+    p.status = ctx->status;
+    p.m = m;
+    p.n = n;
+    p.k = k;
+    p.ldc = ldc;
+    p.alpha = alpha;
+    p.beta = beta;
+    const size_t csz = dtype_size(c_dtype);
+    p.c_vec = (reinterpret_cast<uintptr_t>(c) % 16 == 0 && (static_cast<size_t>(ldc) * csz) % 16 == 0)
+                  ? 1
+                  : 0;
+    p.epi_mode = epi;
+    p.idesc = ptx::make_idesc_f16(ab_dtype == CKL_F16 ? 0u : 1u, 0u, 1u, plan.pair ? 256u : 128u,
+                                  256u);
+    p.sched = plan.sched;
+    if (plan.workspace_bytes > 0) {
+        if (const int rc = get_workspace(ctx, stream, plan.workspace_bytes, &p.workspace);
+            rc != CKL_OK) {
+            return rc;
+        }
+    }
+    switch (c_dtype) {
+        case CKL_F32: return launch_umma_out<float>(plan.pair, ta, tb, p, plan.grid, stream);
+        case CKL_F16: return launch_umma_out<__half>(plan.pair, ta, tb, p, plan.grid, stream);
+        default: return launch_umma_out<__nv_bfloat16>(plan.pair, ta, tb, p, plan.grid, stream);
+    }
+}
+
+int ensure_staging(Staging* s, size_t bytes) {
+    if (s->bytes >= bytes) {
+        return CKL_OK;
+    }
+    if (s->ptr != nullptr) {
+        CKL_TRY_CUDA(cudaFree(s->ptr));
+        s->ptr = nullptr;
+        s->bytes = 0;
+    }
+    CKL_TRY_CUDA(cudaMalloc(&s->ptr, bytes));
+    s->bytes = bytes;
+    return CKL_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ckl_gemm_ex(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, int m, int n,
+                int k, int lda, int ldb, int ldc, float alpha, float beta, int algo,
+                ckl_stream_t stream) {
+    return gemm_impl(ab_dtype, a, b, c, c_dtype, nullptr, m, n, k, lda, ldb, ldc, alpha, beta,
+                     kEpiLinear, algo, static_cast<cudaStream_t>(stream));
+}
+
+int ckl_gemm_f16(const void* a, const void* b, void* c, int c_dtype, int m, int n, int k, int lda,
+                 int ldb, int ldc, float alpha, float beta, ckl_stream_t stream) {
+    return ckl_gemm_ex(CKL_F16, a, b, c, c_dtype, m, n, k, lda, ldb, ldc, alpha, beta,
+                       CKL_ALGO_AUTO, stream);
+}
+
+int ckl_gemm_bf16(const void* a, const void* b, void* c, int c_dtype, int m, int n, int k, int lda,
+                  int ldb, int ldc, float alpha, float beta, ckl_stream_t stream) {
+    return ckl_gemm_ex(CKL_BF16, a, b, c, c_dtype, m, n, k, lda, ldb, ldc, alpha, beta,
+                       CKL_ALGO_AUTO, stream);
+}
+
+int ckl_gemm_bias_relu_ex(int ab_dtype, const void* a, const void* b, void* c, int c_dtype,
+                          const float* bias, int m, int n, int k, int lda, int ldb, int ldc,
+                          float alpha, int algo, ckl_stream_t stream) {
+    return gemm_impl(ab_dtype, a, b, c, c_dtype, bias, m, n, k, lda, ldb, ldc, alpha, 0.0f,
+                     kEpiBiasRelu, algo, static_cast<cudaStream_t>(stream));
+}
+
+int ckl_bias_relu_f32(float* c, const float* bias, int m, int n, int ldc, ckl_stream_t stream) {
+    if (m <= 0 || n <= 0) {
+        return CKL_OK;
+    }
+    if (c == nullptr || bias == nullptr || ldc < n) {
+        return fail(CKL_ERR_INVALID_ARG, "ckl_bias_relu_f32: null pointer or ldc < n");
+    }
+    const long long total = static_cast<long long>(m) * n;
+    const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148LL * 16));
+    bias_relu_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(c, bias, m, n, ldc);
+    CKL_TRY_CUDA(cudaGetLastError());
+    return CKL_OK;
+}
+
+int ckl_gemm_host(int ab_dtype, const void* a_host, const void* b_host, void* c_host, int c_dtype,
+                  int m, int n, int k, float alpha, float beta) {
+    if (m <= 0 || n <= 0) {
+        return CKL_OK;
+    }
+    if (c_host == nullptr || (k > 0 && (a_host == nullptr || b_host == nullptr))) {
+        return fail(CKL_ERR_INVALID_ARG, "ckl_gemm_host: null host pointer");
+    }
+    if (c_dtype != CKL_F32 && c_dtype != CKL_F16 && c_dtype != CKL_BF16) {
+        return fail(CKL_ERR_INVALID_ARG, "C dtype must be CKL_F32, CKL_F16 or CKL_BF16");
+    }
+    DeviceCtx* ctx = nullptr;
+    if (const int rc = get_ctx(&ctx); rc != CKL_OK) {
+        return rc;
+    }
+    std::unique_lock<std::mutex> lock(ctx->mu);
+    if (ctx->host_stream == nullptr) {
+        CKL_TRY_CUDA(cudaStreamCreateWithFlags(&ctx->host_stream, cudaStreamNonBlocking));
+    }
+    const size_t a_bytes = static_cast<size_t>(m) * std::max(k, 0) * 2;
+    const size_t b_bytes = static_cast<size_t>(std::max(k, 0)) * n * 2;
+    const size_t c_bytes = static_cast<size_t>(m) * n * dtype_size(c_dtype);
+    if (int rc = ensure_staging(&ctx->host_a, std::max<size_t>(a_bytes, 16)); rc != CKL_OK) return rc;
+    if (int rc = ensure_staging(&ctx->host_b, std::max<size_t>(b_bytes, 16)); rc != CKL_OK) return rc;
+    if (int rc = ensure_staging(&ctx->host_c, c_bytes); rc != CKL_OK) return rc;
+    cudaStream_t s = ctx->host_stream;
+    if (a_bytes > 0) {
+        CKL_TRY_CUDA(cudaMemcpyAsync(ctx->host_a.ptr, a_host, a_bytes, cudaMemcpyHostToDevice, s));
+    }
+    if (b_bytes > 0) {
+        CKL_TRY_CUDA(cudaMemcpyAsync(ctx->host_b.ptr, b_host, b_bytes, cudaMemcpyHostToDevice, s));
+    }
+    if (beta != 0.0f) {
+        CKL_TRY_CUDA(cudaMemcpyAsync(ctx->host_c.ptr, c_host, c_bytes, cudaMemcpyHostToDevice, s));
+    }
+    // gemm_impl takes ctx->mu only inside get_workspace; release ours first.
+    lock.unlock();
+    const int rc = gemm_impl(ab_dtype, ctx->host_a.ptr, ctx->host_b.ptr, ctx->host_c.ptr, c_dtype,
+                             nullptr, m, n, k, k, n, n, alpha, beta, kEpiLinear, CKL_ALGO_AUTO, s);
+    lock.lock();
+    if (rc != CKL_OK) {
+        return rc;
+    }
+    CKL_TRY_CUDA(cudaMemcpyAsync(c_host, ctx->host_c.ptr, c_bytes, cudaMemcpyDeviceToHost, s));
+    CKL_TRY_CUDA(cudaStreamSynchronize(s));
+    return CKL_OK;
+}
+
+int ckl_plan_gemm(int m, int n, int k, int lda, int ldb, int ldc, int a_align, int b_align,
+                  int algo, int sm_count, ckl_plan* out) {
+    if (out == nullptr) {
+        return fail(CKL_ERR_INVALID_ARG, "ckl_plan_gemm: out is null");
+    }
+    std::memset(out, 0, sizeof *out);
+    if (m <= 0 || n <= 0 || k <= 0) {
+        out->algo = CKL_ALGO_SIMT;  // degenerate: no tiles (k <= 0 runs the scale kernel)
+        return CKL_OK;
+    }
+    if (lda < k || ldb < n || ldc < n) {
+        return fail(CKL_ERR_INVALID_ARG, "leading dimension smaller than the row length");
+    }
+    Plan plan;
+    if (const int rc = make_plan(m, n, k, lda, ldb, static_cast<size_t>(a_align),
+                                 static_cast<size_t>(b_align), algo, sm_count, sm_count / 2, &plan);
+        rc != CKL_OK) {
+        return rc;
+    }
+    out->algo = plan.algo;
+    out->tile_m = plan.tile_m;
+    out->tile_n = plan.tile_n;
+    out->tile_k = plan.tile_k;
+    out->tiles_m = plan.sched.tiles_m;
+    out->tiles_n = plan.sched.tiles_n;
+    out->k_blocks = plan.sched.k_blocks;
+    out->grid = plan.grid;
+    out->dp_tiles = plan.sched.dp_tiles;
+    out->sk_tiles = plan.sched.sk_tiles;
+    out->sk_units = plan.sched.sk_tiles > 0 ? plan.sched.units : 0;
+    out->sk_iters = plan.sched.sk_iters;
+    out->workspace_bytes = plan.workspace_bytes;
+    return CKL_OK;
+}
+
+int ckl_plan_sk_range(const ckl_plan* plan, int u, long long* begin, long long* end) {
+    if (plan == nullptr || begin == nullptr || end == nullptr || plan->sk_units <= 0 || u < 0 ||
+        u >= plan->sk_units) {
+        return fail(CKL_ERR_INVALID_ARG, "ckl_plan_sk_range: bad plan or unit index");
+    }
+    Schedule s = {};
+    s.units = plan->sk_units;
+    s.sk_iters = plan->sk_iters;
+    *begin = sk_range_begin(s, u);
+    *end = sk_range_begin(s, u + 1);
+    return CKL_OK;
+}
+
+int ckl_device_status(unsigned int* info) {
+    DeviceCtx* ctx = nullptr;
+    if (const int rc = get_ctx(&ctx); rc != CKL_OK) {
+        return rc;
+    }
+    CKL_TRY_CUDA(cudaDeviceSynchronize());
+    unsigned int words[4] = {0, 0, 0, 0};
+    CKL_TRY_CUDA(cudaMemcpy(words, ctx->status, sizeof words, cudaMemcpyDeviceToHost));
+    if (info != nullptr) {
+        std::memcpy(info, words, sizeof words);
+    }
+    if (words[0] != 0) {
+        CKL_TRY_CUDA(cudaMemset(ctx->status, 0, sizeof words));
+        return fail(CKL_ERR_DEVICE,
+                    "a kernel gave up a bounded wait: code=%u block=%u role=%u detail=0x%x",
+                    words[0], words[1], words[2], words[3]);
+    }
+    return CKL_OK;
+}
+
+int ckl_stream_copy(void* dst, const void* src, size_t bytes, ckl_stream_t stream) {
+    if (bytes == 0) {
+        return CKL_OK;
+    }
+    if (dst == nullptr || src == nullptr || bytes % 16 != 0 ||
+        reinterpret_cast<uintptr_t>(dst) % 16 != 0 || reinterpret_cast<uintptr_t>(src) % 16 != 0) {
+        return fail(CKL_ERR_INVALID_ARG,
+                    "ckl_stream_copy needs 16-byte aligned pointers and a multiple of 16 bytes");
+    }
+    DeviceCtx* ctx = nullptr;
+    if (const int rc = get_ctx(&ctx); rc != CKL_OK) {
+        return rc;
+    }
+    stream_copy_kernel<<<ctx->sm_count * 4, 512, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint4*>(dst), static_cast<const uint4*>(src), bytes / 16);
+    CKL_TRY_CUDA(cudaGetLastError());
+    return CKL_OK;
+}
+
+const char* ckl_last_error(void) { return g_last_error.c_str(); }
+
+const char* ckl_algo_name(int algo) {
+    switch (algo) {
+        case CKL_ALGO_AUTO: return "auto";
+        case CKL_ALGO_SIMT: return "simt";
+        case CKL_ALGO_UMMA_1CTA: return "umma_1cta";
+        case CKL_ALGO_UMMA_SK: return "umma_1cta_streamk";
+        case CKL_ALGO_UMMA_2CTA: return "umma_2cta";
+        case CKL_ALGO_UMMA_2CTA_SK: return "umma_2cta_streamk";
+        default: return "unknown";
+    }
+}
+
+void ckl_shutdown(void) {
+    std::lock_guard<std::mutex> lock(g_ctx_mu);
+    int prev = 0;
+    const bool have_prev = cudaGetDevice(&prev) == cudaSuccess;
+    for (auto& kv : g_ctx) {
+        DeviceCtx* ctx = kv.second.get();
+        if (cudaSetDevice(ctx->device) != cudaSuccess) {
+            continue;
+        }
+        cudaDeviceSynchronize();
+        for (auto& w : ctx->workspace) {
+            cudaFree(w.second.ptr);
+        }
+        cudaFree(ctx->host_a.ptr);
+        cudaFree(ctx->host_b.ptr);
+        cudaFree(ctx->host_c.ptr);
+        cudaFree(ctx->status);
+        if (ctx->host_stream != nullptr) {
+            cudaStreamDestroy(ctx->host_stream);
+        }
+    }
+    g_ctx.clear();
+    if (have_prev) {
+        cudaSetDevice(prev);
+    }
+}
+
+}  // extern "C"

@@ -1,0 +1,188 @@
+// General-shape GEMM on the CUDA cores: any m, n, k, any leading dimension and
+// any pointer alignment, FP16/BF16 inputs, FP32 accumulation.  It takes the
+// shapes TMA cannot describe (row pitch not a multiple of 16 bytes, unaligned
+// base), the role the scalar half_naive_kernel plays in the reference
+// (include/ckl/detail/wmma_gemm.cuh:124-140), but tiled through shared memory:
+// 64 x 64 output tile, 16-deep k slab, 4 x 4 outputs per thread.
+//
+// Also here: C = beta * C for an empty contraction (k <= 0), the unfused
+// bias + ReLU pass, and the stream-copy bandwidth probe.
+#pragma once
+
+#include <cstdint>
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "gemm_umma.cuh"
+
+namespace ckl {
+
+namespace detail {
+__device__ __forceinline__ float in_to_float(__half v) { return __half2float(v); }
+__device__ __forceinline__ float in_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+}  // namespace detail
+
+template <typename InT, typename OutT>
+__global__ void __launch_bounds__(256)
+simt_gemm_kernel(const InT* __restrict__ a, const InT* __restrict__ b, OutT* c,
+                 const float* __restrict__ bias, int m, int n, int k, int lda, int ldb, int ldc,
+                 float alpha, float beta, int epi_mode) {
+    constexpr int BM = 64, BN = 64, BK = 16;
+    __shared__ float sa[BK][BM + 4];  // transposed: sa[kk][row]
+    __shared__ float sb[BK][BN + 4];
+
+    const int tid = static_cast<int>(threadIdx.x);
+    const int tx = tid % 16;  // column group
+    const int ty = tid / 16;  // row group
+    const int row0 = static_cast<int>(blockIdx.y) * BM;
+    const int col0 = static_cast<int>(blockIdx.x) * BN;
+
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            acc[i][j] = 0.0f;
+        }
+    }
+
+    for (int k0 = 0; k0 < k; k0 += BK) {
+        // A slab: 64 rows x 16 k; thread loads 4 elements (consecutive k of one row).
+        {
+            const int r = tid / 4;
+            const int kk = (tid % 4) * 4;
+            const int gr = row0 + r;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int gk = k0 + kk + e;
+                float v = 0.0f;
+                if (gr < m && gk < k) {
+                    v = detail::in_to_float(a[static_cast<size_t>(gr) * lda + gk]);
+                }
+                sa[kk + e][r] = v;
+            }
+        }
+        // B slab: 16 k x 64 columns; thread loads 4 consecutive columns of one k row.
+        {
+            const int kk = tid / 16;
+            const int cc = (tid % 16) * 4;
+            const int gk = k0 + kk;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int gc = col0 + cc + e;
+                float v = 0.0f;
+                if (gk < k && gc < n) {
+                    v = detail::in_to_float(b[static_cast<size_t>(gk) * ldb + gc]);
+                }
+                sb[kk][cc + e] = v;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float av[4], bv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                av[i] = sa[kk][ty * 4 + i];
+                bv[i] = sb[kk][tx * 4 + i];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    using T = detail::OutTraits<OutT>;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int gr = row0 + ty * 4 + i;
+        if (gr >= m) {
+            continue;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int gc = col0 + tx * 4 + j;
+            if (gc >= n) {
+                continue;
+            }
+            OutT* dst = c + static_cast<size_t>(gr) * ldc + gc;
+            float v;
+            if (epi_mode == kEpiBiasRelu) {
+                v = fmaxf(alpha * acc[i][j] + bias[gc], 0.0f);
+            } else if (beta != 0.0f) {
+                v = alpha * acc[i][j] + beta * T::load(dst);
+            } else {
+                v = alpha * acc[i][j];
+            }
+            T::store(dst, v);
+        }
+    }
+}
+
+// k <= 0: C = beta * C (C = 0 when beta == 0, without reading C), as the
+// reference's kernels and oracle do (include/ckl/detail/wmma_gemm.cuh:133-139,
+// src/gemm/cublas_gemm_ex.cpp:46-50).  With the bias epilogue the empty
+// product gives relu(bias).
+template <typename OutT>
+__global__ void scale_c_kernel(OutT* c, const float* bias, int m, int n, int ldc, float beta,
+                               int epi_mode) {
+    using T = detail::OutTraits<OutT>;
+    const long long total = static_cast<long long>(m) * n;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int r = static_cast<int>(i / n);
+        const int col = static_cast<int>(i % n);
+        OutT* dst = c + static_cast<size_t>(r) * ldc + col;
+        float v;
+        if (epi_mode == kEpiBiasRelu) {
+            v = fmaxf(bias[col], 0.0f);
+        } else {
+            v = beta != 0.0f ? beta * T::load(dst) : 0.0f;
+        }
+        T::store(dst, v);
+    }
+}
+
+// Unfused second pass C = relu(C + bias[col]) over FP32 C; replaces
+// bias_relu_kernel (src/gemm/gemm_mma_opt.cu:199-206).
+__global__ void bias_relu_kernel(float* c, const float* __restrict__ bias, int m, int n, int ldc) {
+    const long long total = static_cast<long long>(m) * n;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int r = static_cast<int>(i / n);
+        const int col = static_cast<int>(i % n);
+        float* dst = c + static_cast<size_t>(r) * ldc + col;
+        *dst = fmaxf(*dst + bias[col], 0.0f);
+    }
+}
+
+// Bandwidth probe: grid-stride 16-byte copy with four independent loads in
+// flight per thread (HBM3e needs far more bytes in flight per SM than the
+// reference's one-load-per-iteration loop, src/tools/device_probe.cu:25-31).
+__global__ void __launch_bounds__(512)
+stream_copy_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, size_t count) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < count; i += 4 * stride) {
+        const uint4 v0 = src[i];
+        const uint4 v1 = src[i + stride];
+        const uint4 v2 = src[i + 2 * stride];
+        const uint4 v3 = src[i + 3 * stride];
+        dst[i] = v0;
+        dst[i + stride] = v1;
+        dst[i + 2 * stride] = v2;
+        dst[i + 3 * stride] = v3;
+    }
+    for (; i < count; i += stride) {
+        dst[i] = src[i];
+    }
+}
+
+}  // namespace ckl

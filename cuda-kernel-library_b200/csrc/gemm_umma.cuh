@@ -1,0 +1,706 @@
+// Tensor-core GEMM for sm_100a: TMA-fed shared-memory ring, tcgen05.mma
+// accumulating in tensor memory, warp-specialised persistent CTAs.
+//
+// Replaces the reference's whole FP16/BF16 ladder (wmma_gemm_kernel,
+// include/ckl/detail/wmma_gemm.cuh:49-119; gemm_mma_ptx_kernel,
+// src/gemm/gemm_mma_ptx.cu:50-136; gemm_mma_ldmatrix_kernel,
+// src/gemm/gemm_mma_ldmatrix.cu:60-133; gemm_mma_opt_kernel,
+// src/gemm/gemm_mma_opt.cu:87-195).  It shares nothing with them: there is no
+// mma.sync, ldmatrix or cp.async here.
+//
+// One kernel template, two shapes of worker ("unit"):
+//
+//   kPair = false   one CTA per unit, output tile 128 x 256, UMMA 128x256x16,
+//                   4-stage ring of (A 128x64, B 64x256) = 48 KB per stage.
+//   kPair = true    a cluster of two CTAs per unit, output tile 256 x 256,
+//                   UMMA 256x256x16 issued by the leader CTA for both SMs
+//                   (cta_group::2).  Each CTA loads only its own 128 rows of A
+//                   and its own 128 columns of B (no multicast), 32 KB per
+//                   stage, 6 stages.
+//
+// Data layout.  A is row-major m x k, so a 128 x 64 box lands in shared memory
+// K-major: 128 rows of 128 bytes under the 128-byte swizzle.  B is row-major
+// k x n, i.e. N-major; a stage holds 64-column boxes of 64 k-rows x 128 bytes,
+// also 128-byte swizzled, and the MMA reads them through an MN-major
+// descriptor (leading offset = one box, stride offset = 8 k-rows), so B is
+// never transposed in memory.  TMA zero-fills whatever lies outside the
+// matrix, which is what makes ragged m, n and k work: zero rows of A and zero
+// k-rows contribute nothing and the epilogue predicates its stores.
+//
+// Warp roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = MMA
+// issuer (one lane) and TMEM owner, warps 2-5 = epilogue (each reads the TMEM
+// lane quarter its warp id selects).  The 512 TMEM columns hold two 256-column
+// accumulators so the epilogue of one tile overlaps the main loop of the next.
+//
+// Every wait on an mbarrier is bounded: after kWaitLimitNs the waiter records
+// a code in the status word, raises the CTA's abort flag (and the peer's), and
+// every role falls through to the common exit, which drains in-flight copies
+// and MMAs, frees TMEM and returns.  Nothing traps or spins without limit.
+#pragma once
+
+#include <cstdint>
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "ptx.cuh"
+#include "tile_sched.h"
+
+namespace ckl {
+
+enum EpilogueMode : int { kEpiLinear = 0, kEpiBiasRelu = 1 };
+
+struct GemmParams {
+    void* c;              // output, OutT, row-major, leading dimension ldc
+    const float* bias;    // n floats (kEpiBiasRelu) or nullptr
+    float* workspace;     // partial-tile slots (stream-K) or nullptr
+    unsigned int* status; // 4 words: code, block, role, detail
+    int m, n, k;
+    int ldc;
+    float alpha, beta;
+    int c_vec;            // 16-byte vector access to C is legal
+    int epi_mode;
+    uint32_t idesc;
+    Schedule sched;
+};
+
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+
+enum StatusCode : unsigned int {
+    kStatusOk = 0,
+    kStatusWaitTimeout = 1,
+};
+enum Role : unsigned int { kRoleProducer = 1, kRoleMma = 2, kRoleEpilogue = 3, kRoleDrain = 4 };
+
+template <bool kPair>
+struct UmmaConfig {
+    static constexpr int kStages = kPair ? 6 : 4;
+    static constexpr int kBBoxes = kPair ? 2 : 4;  // 64-column boxes of B per CTA per stage
+    static constexpr uint32_t kABytes = 128 * 64 * 2;
+    static constexpr uint32_t kBoxBytes = 64 * 64 * 2;
+    static constexpr uint32_t kBBytes = kBBoxes * kBoxBytes;
+    static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+    static constexpr uint32_t kTxBytes = kStageBytes * (kPair ? 2 : 1);
+    static constexpr int kTileM = kPair ? 256 : 128;
+    static constexpr int kTileN = 256;
+    static constexpr int kTileK = 64;
+    static constexpr int kNumBarriers = 2 * kStages + 5;
+    // ring + barriers + TMEM slot + abort flag, plus slack to 1024-align the ring
+    static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kNumBarriers * 8 + 16 + 1024;
+    static constexpr int kThreads = 192;
+    static constexpr size_t kSlotFloats = static_cast<size_t>(kTileM) * kTileN;
+};
+
+namespace detail {
+
+struct Control {
+    volatile int* abort_flag;   // this CTA's flag (generic pointer into shared memory)
+    uint32_t abort_flag_smem;   // same, as a shared-window address
+    unsigned int* status;
+    bool pair;
+    uint32_t peer_rank;
+};
+
+__device__ __forceinline__ void raise_abort(const Control& ctl, unsigned int role,
+                                            unsigned int detail_word) {
+    *ctl.abort_flag = 1;
+    if (ctl.pair) {
+        const uint32_t remote = ptx::map_to_cta(ctl.abort_flag_smem, ctl.peer_rank);
+        asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote), "r"(1u) : "memory");
+    }
+    if (atomicCAS(ctl.status, 0u, static_cast<unsigned int>(kStatusWaitTimeout)) == 0u) {
+        ctl.status[1] = blockIdx.x;
+        ctl.status[2] = role;
+        ctl.status[3] = detail_word;
+        __threadfence();
+    }
+}
+
+// Bounded wait.  Returns false when the limit ran out here or another role
+// already aborted; the caller must then leave its loop.
+__device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, const Control& ctl,
+                                             unsigned int role, unsigned int detail_word) {
+    if (ptx::mbar_try_wait(bar, parity)) {
+        return true;
+    }
+    unsigned long long t0 = 0;
+    unsigned int spins = 0;
+    while (true) {
+        if (ptx::mbar_try_wait(bar, parity)) {
+            return true;
+        }
+        if ((++spins & 127u) == 0u) {
+            if (*ctl.abort_flag != 0) {
+                return false;
+            }
+            const unsigned long long now = ptx::global_timer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > kWaitLimitNs) {
+                raise_abort(ctl, role, detail_word);
+                return false;
+            }
+        }
+    }
+}
+
+// Short bounded wait used only while draining on the way out: never raises.
+__device__ __forceinline__ void drain_wait(uint32_t bar, uint32_t parity) {
+    const unsigned long long t0 = ptx::global_timer_ns();
+    for (unsigned int i = 0;; ++i) {
+        if (ptx::mbar_try_wait(bar, parity)) {
+            return;
+        }
+        if ((i & 63u) == 63u && ptx::global_timer_ns() - t0 > 20000000ull) {  // 20 ms
+            return;
+        }
+    }
+}
+
+template <typename OutT>
+struct OutTraits;
+template <>
+struct OutTraits<float> {
+    static constexpr int kVec = 4;
+    static __device__ __forceinline__ float load(const float* p) { return *p; }
+    static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+    static __device__ __forceinline__ void load_vec(const float* p, float (&v)[4]) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    }
+    static __device__ __forceinline__ void store_vec(float* p, const float* v) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <>
+struct OutTraits<__half> {
+    static constexpr int kVec = 8;
+    static __device__ __forceinline__ float load(const __half* p) { return __half2float(*p); }
+    static __device__ __forceinline__ void store(__half* p, float v) { *p = __float2half_rn(v); }
+    static __device__ __forceinline__ void load_vec(const __half* p, float (&v)[8]) {
+        const uint4 t = *reinterpret_cast<const uint4*>(p);
+        const __half2* h = reinterpret_cast<const __half2*>(&t);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h[i]);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store_vec(__half* p, const float* v) {
+        uint4 t;
+        __half2* h = reinterpret_cast<__half2*>(&t);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        }
+        *reinterpret_cast<uint4*>(p) = t;
+    }
+};
+template <>
+struct OutTraits<__nv_bfloat16> {
+    static constexpr int kVec = 8;
+    static __device__ __forceinline__ float load(const __nv_bfloat16* p) {
+        return __bfloat162float(*p);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) {
+        *p = __float2bfloat16_rn(v);
+    }
+    static __device__ __forceinline__ void load_vec(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 t = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&t);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h[i]);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store_vec(__nv_bfloat16* p, const float* v) {
+        uint4 t;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&t);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        }
+        *reinterpret_cast<uint4*>(p) = t;
+    }
+};
+
+// The epilogue arithmetic on 32 consecutive columns of one output row:
+// acc (FP32 accumulators) -> alpha / beta / bias / relu -> OutT, stores
+// predicated on n.  `row_ptr` points at column 0 of the row in C.
+template <typename OutT>
+__device__ __forceinline__ void finish_row_chunk(float (&acc)[32], OutT* row_ptr, int col0, int n,
+                                                 float alpha, float beta, const float* bias,
+                                                 int epi_mode, bool vec_ok) {
+    using T = OutTraits<OutT>;
+    constexpr int V = T::kVec;
+    if (col0 >= n) {
+        return;
+    }
+#pragma unroll
+    for (int g = 0; g < 32 / V; ++g) {
+        const int col = col0 + g * V;
+        if (col >= n) {
+            break;
+        }
+        const bool full = vec_ok && (col + V <= n);
+        float out[V];
+        if (epi_mode == kEpiBiasRelu) {
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                const float bv = (col + e < n) ? __ldg(bias + col + e) : 0.0f;
+                out[e] = fmaxf(alpha * acc[g * V + e] + bv, 0.0f);
+            }
+        } else if (beta != 0.0f) {
+            float cin[V];
+            if (full) {
+                T::load_vec(row_ptr + col, cin);
+            } else {
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    cin[e] = (col + e < n) ? T::load(row_ptr + col + e) : 0.0f;
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                out[e] = alpha * acc[g * V + e] + beta * cin[e];
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                out[e] = alpha * acc[g * V + e];
+            }
+        }
+        if (full) {
+            T::store_vec(row_ptr + col, out);
+        } else {
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                if (col + e < n) {
+                    T::store(row_ptr + col + e, out[e]);
+                }
+            }
+        }
+    }
+}
+
+}  // namespace detail
+
+template <bool kPair, typename OutT>
+__global__ void __launch_bounds__(192, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                 const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+    using Cfg = UmmaConfig<kPair>;
+    constexpr int kStages = Cfg::kStages;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t ring = (raw_addr + 1023u) & ~1023u;
+    uint8_t* ring_ptr = smem_raw + (ring - raw_addr);
+    const uint32_t bars = ring + kStages * Cfg::kStageBytes;
+    uint8_t* bars_ptr = ring_ptr + kStages * Cfg::kStageBytes;
+
+    auto full_bar = [&](int s) { return bars + 8u * static_cast<uint32_t>(s); };
+    auto empty_bar = [&](int s) { return bars + 8u * static_cast<uint32_t>(kStages + s); };
+    auto acc_full_bar = [&](int a) { return bars + 8u * static_cast<uint32_t>(2 * kStages + a); };
+    auto acc_empty_bar = [&](int a) {
+        return bars + 8u * static_cast<uint32_t>(2 * kStages + 2 + a);
+    };
+    const uint32_t drain_bar = bars + 8u * static_cast<uint32_t>(2 * kStages + 4);
+    const uint32_t tmem_slot = bars + 8u * static_cast<uint32_t>(Cfg::kNumBarriers);
+    volatile uint32_t* tmem_slot_ptr =
+        reinterpret_cast<volatile uint32_t*>(bars_ptr + 8 * Cfg::kNumBarriers);
+
+    detail::Control ctl;
+    ctl.abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 8 * Cfg::kNumBarriers + 4);
+    ctl.abort_flag_smem = tmem_slot + 4u;
+    ctl.status = p.status;
+    ctl.pair = kPair;
+
+    const int warp = static_cast<int>(threadIdx.x >> 5);
+    const uint32_t lane = ptx::lane_id();
+    const uint32_t rank = kPair ? ptx::cluster_cta_rank() : 0u;
+    ctl.peer_rank = rank ^ 1u;
+    const int unit = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const bool leader = (rank == 0u);
+
+    // ---- set-up ---------------------------------------------------------------
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(acc_full_bar(a), 1);
+            ptx::mbar_init(acc_empty_bar(a), kPair ? 8 : 4);
+        }
+        ptx::mbar_init(drain_bar, 1);
+        *ctl.abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {
+        if constexpr (kPair) {
+            ptx::tmem_alloc_pair(tmem_slot, 512);
+            ptx::tmem_relinquish_pair();
+        } else {
+            ptx::tmem_alloc(tmem_slot, 512);
+            ptx::tmem_relinquish();
+        }
+    }
+    ptx::tc_fence_before_sync();
+    if constexpr (kPair) {
+        ptx::cluster_arrive_release();
+        ptx::cluster_wait_acquire();
+    } else {
+        __syncthreads();
+    }
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    const Schedule& sched = p.sched;
+
+    // ---- roles ----------------------------------------------------------------
+    if (warp == 0) {
+        if (lane == 0) {
+            // TMA producer.
+            SegmentCursor cur = make_cursor(sched, unit);
+            Segment seg;
+            uint32_t it = 0;
+            bool ok = true;
+            while (ok && next_segment(sched, &cur, &seg)) {
+                int tm, tn;
+                tile_coords(sched, seg.tile, &tm, &tn);
+                const int a_row = tm * Cfg::kTileM + (kPair ? static_cast<int>(rank) * 128 : 0);
+                const int b_col = tn * Cfg::kTileN + (kPair ? static_cast<int>(rank) * 128 : 0);
+                for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb) {
+                    const int s = static_cast<int>(it % kStages);
+                    const uint32_t use = it / kStages;
+                    if (!detail::wait_barrier(empty_bar(s), (use & 1u) ^ 1u, ctl, kRoleProducer,
+                                              it)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = ring + static_cast<uint32_t>(s) * Cfg::kStageBytes;
+                    const uint32_t b_dst = a_dst + Cfg::kABytes;
+                    if constexpr (kPair) {
+                        if (leader) {
+                            ptx::mbar_arrive_expect_tx(full_bar(s), Cfg::kTxBytes);
+                        }
+                        const uint32_t bar = ptx::map_to_cta(full_bar(s), 0);
+                        ptx::tma_load_2d_pair(a_dst, &tmap_a, bar, kb * 64, a_row);
+#pragma unroll
+                        for (int j = 0; j < Cfg::kBBoxes; ++j) {
+                            ptx::tma_load_2d_pair(b_dst + j * Cfg::kBoxBytes, &tmap_b, bar,
+                                                  b_col + j * 64, kb * 64);
+                        }
+                    } else {
+                        ptx::mbar_arrive_expect_tx(full_bar(s), Cfg::kTxBytes);
+                        ptx::tma_load_2d(a_dst, &tmap_a, full_bar(s), kb * 64, a_row);
+#pragma unroll
+                        for (int j = 0; j < Cfg::kBBoxes; ++j) {
+                            ptx::tma_load_2d(b_dst + j * Cfg::kBoxBytes, &tmap_b, full_bar(s),
+                                             b_col + j * 64, kb * 64);
+                        }
+                    }
+                    ++it;
+                }
+            }
+            // Tail: do not leave while the consumer may still signal this CTA's
+            // empty barriers or copies into this CTA's ring are in flight.
+            const uint32_t first = it > static_cast<uint32_t>(kStages) ? it - kStages : 0u;
+            for (uint32_t i = first; i < it; ++i) {
+                const int s = static_cast<int>(i % kStages);
+                const uint32_t use = i / kStages;
+                if (ok) {
+                    if (!detail::wait_barrier(empty_bar(s), use & 1u, ctl, kRoleDrain, i)) {
+                        ok = false;
+                    }
+                }
+                if (!ok) {
+                    // Aborting: only make sure our own copies have landed.
+                    if (!kPair || leader) {
+                        detail::drain_wait(full_bar(s), use & 1u);
+                    } else {
+                        __nanosleep(20000);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            // MMA issuer.
+            SegmentCursor cur = make_cursor(sched, unit);
+            Segment seg;
+            uint32_t it = 0;
+            uint32_t seg_count = 0;
+            bool ok = true;
+            while (ok && next_segment(sched, &cur, &seg)) {
+                const uint32_t acc = seg_count & 1u;
+                const uint32_t acc_use = seg_count >> 1;
+                if (!detail::wait_barrier(acc_empty_bar(acc), (acc_use & 1u) ^ 1u, ctl, kRoleMma,
+                                          0x80000000u | seg_count)) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * 256u;
+                for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb) {
+                    const int s = static_cast<int>(it % kStages);
+                    const uint32_t use = it / kStages;
+                    if (!detail::wait_barrier(full_bar(s), use & 1u, ctl, kRoleMma, it)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t a_src = ring + static_cast<uint32_t>(s) * Cfg::kStageBytes;
+                    const uint32_t b_src = a_src + Cfg::kABytes;
+                    // A: K-major, 8-row groups 1024 B apart.  B: N-major, 64-column
+                    // boxes 8192 B apart (leading), 8-k-row groups 1024 B apart (stride).
+                    const uint64_t a_desc = ptx::make_smem_desc_sw128(a_src, 16, 1024);
+                    const uint64_t b_desc = ptx::make_smem_desc_sw128(b_src, Cfg::kBoxBytes, 1024);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        // 16 k elements per instruction: +32 B along a K-major row of A,
+                        // +16 k-rows (2048 B) of B.  Descriptor addresses count 16 B.
+                        const uint32_t accumulate = (kb > seg.kb_begin || j > 0) ? 1u : 0u;
+                        if constexpr (kPair) {
+                            ptx::umma_f16_pair(d_tmem, a_desc + static_cast<uint64_t>(j * 2),
+                                               b_desc + static_cast<uint64_t>(j * 128), p.idesc,
+                                               accumulate);
+                        } else {
+                            ptx::umma_f16(d_tmem, a_desc + static_cast<uint64_t>(j * 2),
+                                          b_desc + static_cast<uint64_t>(j * 128), p.idesc,
+                                          accumulate);
+                        }
+                    }
+                    if constexpr (kPair) {
+                        ptx::umma_commit_pair(empty_bar(s));
+                        ptx::umma_commit_pair(ptx::map_to_cta(empty_bar(s), 1));
+                    } else {
+                        ptx::umma_commit(empty_bar(s));
+                    }
+                    ++it;
+                }
+                if (ok) {
+                    if constexpr (kPair) {
+                        ptx::umma_commit_pair(acc_full_bar(acc));
+                        ptx::umma_commit_pair(ptx::map_to_cta(acc_full_bar(acc), 1));
+                    } else {
+                        ptx::umma_commit(acc_full_bar(acc));
+                    }
+                    ++seg_count;
+                }
+            }
+            if (ok) {
+                // Tail: the epilogue (of both CTAs) must have drained the last
+                // accumulators before TMEM can go.
+                const uint32_t first = seg_count > 2u ? seg_count - 2u : 0u;
+                for (uint32_t i = first; i < seg_count && ok; ++i) {
+                    ok = detail::wait_barrier(acc_empty_bar(i & 1u), (i >> 1) & 1u, ctl, kRoleDrain,
+                                              0x80000000u | i);
+                }
+            } else {
+                // Aborting: wait (bounded) until the MMAs already issued have retired.
+                if constexpr (kPair) {
+                    ptx::umma_commit_pair(drain_bar);
+                } else {
+                    ptx::umma_commit(drain_bar);
+                }
+                detail::drain_wait(drain_bar, 0);
+            }
+        }
+    } else {
+        // Epilogue warps 2..5; TMEM lane quarter = warp id mod 4.
+        const uint32_t quad = static_cast<uint32_t>(warp) & 3u;
+        SegmentCursor cur = make_cursor(sched, unit);
+        Segment seg;
+        uint32_t seg_count = 0;
+        OutT* c_base = static_cast<OutT*>(p.c);
+        const bool vec_ok = p.c_vec != 0;
+        while (next_segment(sched, &cur, &seg)) {
+            const uint32_t acc = seg_count & 1u;
+            const uint32_t acc_use = seg_count >> 1;
+            int ok = 1;
+            if (lane == 0) {
+                ok = detail::wait_barrier(acc_full_bar(acc), acc_use & 1u, ctl, kRoleEpilogue,
+                                          seg_count)
+                         ? 1
+                         : 0;
+            }
+            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+            if (!ok) {
+                break;
+            }
+            // Every lane observes the completed phase itself (acquire); it cannot
+            // advance again before this warp releases the accumulator below.
+            for (int i = 0; i < 1024 && !ptx::mbar_try_wait(acc_full_bar(acc), acc_use & 1u); ++i) {
+            }
+            ptx::tc_fence_after_sync();
+
+            int tm, tn;
+            tile_coords(sched, seg.tile, &tm, &tn);
+            const int row_in_tile = (kPair ? static_cast<int>(rank) * 128 : 0) +
+                                    static_cast<int>(quad) * 32 + static_cast<int>(lane);
+            const int row = tm * Cfg::kTileM + row_in_tile;
+            const int col_base = tn * Cfg::kTileN;
+            const uint32_t t_row = tmem_base + ((quad * 32u) << 16) + acc * 256u;
+
+            if (seg.slot >= 0) {
+                // Partial accumulator -> FP32 workspace slot, full tile, no predication.
+                float* dst = p.workspace + static_cast<size_t>(seg.slot) * Cfg::kSlotFloats +
+                             static_cast<size_t>(row_in_tile) * Cfg::kTileN;
+#pragma unroll 1
+                for (int c = 0; c < Cfg::kTileN / 32; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), r);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        *reinterpret_cast<uint4*>(dst + c * 32 + q * 4) =
+                            make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                    }
+                }
+            } else {
+                OutT* row_ptr = c_base + static_cast<size_t>(row) * static_cast<size_t>(p.ldc);
+                const bool row_ok = row < p.m;
+#pragma unroll 1
+                for (int c = 0; c < Cfg::kTileN / 32; ++c) {
+                    if (col_base + c * 32 >= p.n) {
+                        break;  // uniform across the warp
+                    }
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), r);
+                    ptx::tmem_ld_wait();
+                    if (row_ok) {
+                        float acc_f[32];
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            acc_f[e] = __uint_as_float(r[e]);
+                        }
+                        detail::finish_row_chunk<OutT>(acc_f, row_ptr, col_base + c * 32, p.n,
+                                                       p.alpha, p.beta, p.bias, p.epi_mode, vec_ok);
+                    }
+                }
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                if constexpr (kPair) {
+                    ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_empty_bar(acc), 0));
+                } else {
+                    ptx::mbar_arrive(acc_empty_bar(acc));
+                }
+            }
+            ++seg_count;
+        }
+    }
+
+    // ---- common exit ----------------------------------------------------------
+    ptx::tc_fence_before_sync();
+    if constexpr (kPair) {
+        __syncthreads();
+        ptx::cluster_arrive_release();
+        ptx::cluster_wait_acquire();
+    } else {
+        __syncthreads();
+    }
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        if constexpr (kPair) {
+            ptx::tmem_dealloc_pair(tmem_base, 512);
+        } else {
+            ptx::tmem_dealloc(tmem_base, 512);
+        }
+    }
+}
+
+// Fix-up pass of the stream-K split: one CTA per split tile.  Adds the FP32
+// partials of the tile in ascending unit order and applies the epilogue.
+// Tiles that a single unit covered whole were already written by the GEMM
+// kernel and are skipped.
+template <int kTileM, typename OutT>
+__global__ void __launch_bounds__(256)
+streamk_fixup_kernel(const GemmParams p) {
+    constexpr int kTileN = 256;
+    constexpr size_t kSlotFloats = static_cast<size_t>(kTileM) * kTileN;
+    const Schedule& s = p.sched;
+    const int sk_tile = static_cast<int>(blockIdx.x);
+    const long long it0 = static_cast<long long>(sk_tile) * s.k_blocks;
+    const long long it1 = it0 + s.k_blocks;
+
+    __shared__ int slots[512];
+    __shared__ int n_slots;
+    if (threadIdx.x == 0) {
+        int count = 0;
+        int u = sk_owner_of(s, it0);
+        while (u < s.units) {
+            const long long b = sk_range_begin(s, u);
+            const long long e = sk_range_begin(s, u + 1);
+            if (b >= it1) {
+                break;
+            }
+            if (e > it0 && e > b) {
+                const long long lo = b > it0 ? b : it0;
+                const long long hi = e < it1 ? e : it1;
+                if (lo == it0 && hi == it1) {
+                    count = 0;  // one unit owns the whole tile: nothing to add
+                    break;
+                }
+                if (count < 512) {
+                    slots[count++] = 2 * u + (lo == it0 ? 1 : 0);
+                }
+            }
+            ++u;
+        }
+        n_slots = count;
+    }
+    __syncthreads();
+    const int count = n_slots;
+    if (count == 0) {
+        return;
+    }
+    int tm, tn;
+    tile_coords(s, s.dp_tiles + sk_tile, &tm, &tn);
+    OutT* c_base = static_cast<OutT*>(p.c);
+    const bool vec_ok = p.c_vec != 0;
+    // 32-column chunks: kTileM rows x 8 chunks, a warp takes 32 consecutive
+    // chunk-rows so that workspace reads are 128-byte segments per lane.
+    for (int item = static_cast<int>(threadIdx.x); item < kTileM * (kTileN / 32);
+         item += static_cast<int>(blockDim.x)) {
+        const int r = item / (kTileN / 32);
+        const int c = item % (kTileN / 32);
+        const int row = tm * kTileM + r;
+        const int col0 = tn * kTileN + c * 32;
+        if (row >= p.m || col0 >= p.n) {
+            continue;
+        }
+        float acc[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+            acc[e] = 0.0f;
+        }
+        for (int i = 0; i < count; ++i) {
+            const float* src = p.workspace + static_cast<size_t>(slots[i]) * kSlotFloats +
+                               static_cast<size_t>(r) * kTileN + c * 32;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float4 v = *reinterpret_cast<const float4*>(src + q * 4);
+                acc[4 * q] += v.x;
+                acc[4 * q + 1] += v.y;
+                acc[4 * q + 2] += v.z;
+                acc[4 * q + 3] += v.w;
+            }
+        }
+        OutT* row_ptr = c_base + static_cast<size_t>(row) * static_cast<size_t>(p.ldc);
+        detail::finish_row_chunk<OutT>(acc, row_ptr, col0, p.n, p.alpha, p.beta, p.bias, p.epi_mode,
+                                       vec_ok);
+    }
+}
+
+}  // namespace ckl

@@ -1,0 +1,148 @@
+/*
+ * ckl_gemm.h -- C ABI of the B200 (sm_100a) tensor-core GEMM library.
+ *
+ *     C = alpha * (A * B) + beta * C        FP16 or BF16 A and B, FP32 accumulate
+ *
+ * Conventions are the reference library's (include/ckl/gemm.hpp:7-15 there):
+ * row-major storage, A is m x k, B is k x n, C is m x n, no transposes, no
+ * batching, device pointers owned by the caller, work is enqueued on `stream`
+ * and the call returns without synchronising (NULL = the legacy default
+ * stream).  Unlike the reference's C++ launchers the leading dimensions are
+ * explicit, because an N-sharded B or C is a column block of a wider matrix.
+ *
+ * Every function returns a ckl_status (0 = success) and never throws or
+ * aborts; ckl_last_error() gives the message for the calling thread's last
+ * failure.  Degenerate shapes follow the reference
+ * (include/ckl/detail/wmma_gemm.cuh:142-159, src/gemm/cublas_gemm_ex.cpp:41-50):
+ * m <= 0 or n <= 0 is a no-op, k <= 0 computes C = beta * C.  As in BLAS, C is
+ * not read when beta == 0.
+ *
+ * The library links only the CUDA runtime.  There is no CPU fallback: a call
+ * on a machine without an sm_100 GPU fails with CKL_ERR_CUDA /
+ * CKL_ERR_UNSUPPORTED.
+ */
+#ifndef CKL_GEMM_H_
+#define CKL_GEMM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum ckl_status {
+    CKL_OK = 0,
+    CKL_ERR_INVALID_ARG = 1, /* null pointer, bad dtype, leading dimension too small */
+    CKL_ERR_CUDA = 2,        /* a CUDA runtime or driver call failed */
+    CKL_ERR_UNSUPPORTED = 3, /* device is not sm_100, or forced algo cannot run the shape */
+    CKL_ERR_DEVICE = 4,      /* a kernel reported a bounded wait that ran out */
+    CKL_ERR_TOO_LARGE = 5    /* request exceeds a fixed capacity of the entry point */
+} ckl_status;
+
+/* Element types.  A and B are CKL_F16 or CKL_BF16; C may be any of the three. */
+typedef enum ckl_dtype { CKL_F32 = 0, CKL_F16 = 1, CKL_BF16 = 2 } ckl_dtype;
+
+/* Kernel selection.  CKL_ALGO_AUTO is what every reference-named entry point
+ * uses; the others exist so tests and benchmarks can pin one kernel. */
+typedef enum ckl_algo {
+    CKL_ALGO_AUTO = 0,
+    CKL_ALGO_SIMT = 1,       /* general-shape CUDA-core kernel (any size, any alignment) */
+    CKL_ALGO_UMMA_1CTA = 2,  /* TMA + tcgen05.mma, one CTA per 128x256 tile, data-parallel */
+    CKL_ALGO_UMMA_SK = 3,    /* same kernel with the stream-K split of the tile remainder */
+    CKL_ALGO_UMMA_2CTA = 4,  /* CTA-pair tcgen05.mma (cta_group::2), 256x256 tile per pair */
+    CKL_ALGO_UMMA_2CTA_SK = 5
+} ckl_algo;
+
+/* Stream handle: a cudaStream_t passed as an opaque pointer so this header
+ * needs no CUDA include. */
+typedef void* ckl_stream_t;
+
+/* FP16 inputs.  Replaces ckl::gemm_wmma_fp16 / gemm_mma_ptx / gemm_mma_ldm /
+ * gemm_mma_opt of the reference (include/ckl/gemm.hpp:68-69,75-76,80-81,85-86;
+ * definitions src/gemm/gemm_wmma_fp16.cu:8-11, gemm_mma_ptx.cu:144-158,
+ * gemm_mma_ldmatrix.cu:141-153, gemm_mma_opt.cu:214-226), which all compute
+ * the same function with c_dtype = CKL_F32, lda = k, ldb = ldc = n. */
+int ckl_gemm_f16(const void* a, const void* b, void* c, int c_dtype, int m, int n, int k, int lda,
+                 int ldb, int ldc, float alpha, float beta, ckl_stream_t stream);
+
+/* BF16 inputs.  Replaces ckl::gemm_wmma_bf16 (include/ckl/gemm.hpp:70-71,
+ * src/gemm/gemm_wmma_bf16.cu:10-13). */
+int ckl_gemm_bf16(const void* a, const void* b, void* c, int c_dtype, int m, int n, int k, int lda,
+                  int ldb, int ldc, float alpha, float beta, ckl_stream_t stream);
+
+/* Same computation with the input type and the kernel chosen by argument.
+ * Forcing a tensor-core algo on a shape it cannot take (A or B not 16-byte
+ * aligned, lda or ldb not a multiple of 8 elements, k <= 0) returns
+ * CKL_ERR_UNSUPPORTED; CKL_ALGO_AUTO routes such shapes to CKL_ALGO_SIMT the
+ * way the reference routes them to its scalar kernel
+ * (include/ckl/detail/wmma_gemm.cuh:148-158). */
+int ckl_gemm_ex(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, int m, int n,
+                int k, int lda, int ldb, int ldc, float alpha, float beta, int algo,
+                ckl_stream_t stream);
+
+/* Fused epilogue C = relu(alpha * A*B + bias[col]) (C is not read), and the
+ * unfused second pass C = relu(C + bias[col]) over an FP32 C.  Replace
+ * ckl::gemm_mma_opt_bias and ckl::gemm_bias_relu (include/ckl/gemm.hpp:91-93,
+ * src/gemm/gemm_mma_opt.cu:228-246).  bias is n floats on the device. */
+int ckl_gemm_bias_relu_ex(int ab_dtype, const void* a, const void* b, void* c, int c_dtype,
+                          const float* bias, int m, int n, int k, int lda, int ldb, int ldc,
+                          float alpha, int algo, ckl_stream_t stream);
+int ckl_bias_relu_f32(float* c, const float* bias, int m, int n, int ldc, ckl_stream_t stream);
+
+/* Whole call with HOST buffers: copies A, B (and C when beta != 0) to device
+ * memory the library keeps per device, runs the GEMM, copies C back and waits.
+ * This is what a caller holding host matrices pays end to end; it is the
+ * host-side counterpart of the upload / launch / download sequence in the
+ * reference's test driver (tests/test_gemm_tensor.cpp:69-85).  Pinned host
+ * buffers make the copies run at full PCIe rate. */
+int ckl_gemm_host(int ab_dtype, const void* a_host, const void* b_host, void* c_host, int c_dtype,
+                  int m, int n, int k, float alpha, float beta);
+
+/* Host-side planning, no GPU needed: what ckl_gemm_ex would launch for this
+ * shape on a device with `sm_count` SMs.  Mirrors the role of the reference's
+ * launch_wmma dispatch test (include/ckl/detail/wmma_gemm.cuh:148) as a pure
+ * function so it can be unit-tested on a CPU. */
+typedef struct ckl_plan {
+    int algo;           /* resolved ckl_algo */
+    int tile_m, tile_n; /* output tile of one work unit (per CTA pair for 2-CTA) */
+    int tile_k;         /* k elements per pipeline stage */
+    int tiles_m, tiles_n, k_blocks;
+    int grid;           /* CTAs launched */
+    int dp_tiles;       /* tiles computed whole by one CTA (or pair) */
+    int sk_tiles;       /* tiles whose k range is split across CTAs */
+    int sk_units;       /* CTAs (or pairs) sharing the split tiles */
+    long long sk_iters; /* total k-block iterations in the split region */
+    size_t workspace_bytes;
+} ckl_plan;
+int ckl_plan_gemm(int m, int n, int k, int lda, int ldb, int ldc, int a_align, int b_align,
+                  int algo, int sm_count, ckl_plan* out);
+
+/* The k-block range of split tile work owned by unit `u` of a plan:
+ * iterations [*begin, *end) of the sk_iters total.  Exposed for tests. */
+int ckl_plan_sk_range(const ckl_plan* plan, int u, long long* begin, long long* end);
+
+/* Device-side health word.  Kernels never trap or spin forever: a wait that
+ * exceeds its limit records a code here and the kernel drains and exits.
+ * Synchronises the current device, returns CKL_OK or CKL_ERR_DEVICE and
+ * clears the word; info (4 words: code, block, role, detail) may be NULL. */
+int ckl_device_status(unsigned int* info);
+
+/* Stream-copy bandwidth probe used by the roofline tools (replaces
+ * stream_copy in src/tools/device_probe.cu:25-70): copies `bytes` from src
+ * to dst on the device with a grid sized for HBM3e. */
+int ckl_stream_copy(void* dst, const void* src, size_t bytes, ckl_stream_t stream);
+
+/* Message of the calling thread's most recent non-zero status ("" if none). */
+const char* ckl_last_error(void);
+
+/* Name of a ckl_algo value, e.g. "umma_1cta". */
+const char* ckl_algo_name(int algo);
+
+/* Frees every per-device cache (workspaces, staging buffers). */
+void ckl_shutdown(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CKL_GEMM_H_ */
