@@ -40,7 +40,8 @@ class Plan(ctypes.Structure):
     _fields_ = [
         ("algo", ctypes.c_int), ("tile_m", ctypes.c_int), ("tile_n", ctypes.c_int),
         ("tile_k", ctypes.c_int), ("tiles_m", ctypes.c_int), ("tiles_n", ctypes.c_int),
-        ("k_blocks", ctypes.c_int), ("grid", ctypes.c_int), ("dp_tiles", ctypes.c_int),
+        ("k_blocks", ctypes.c_int), ("grid", ctypes.c_int), ("units", ctypes.c_int),
+        ("group_m", ctypes.c_int), ("dp_tiles", ctypes.c_int),
         ("sk_tiles", ctypes.c_int), ("sk_units", ctypes.c_int), ("sk_iters", ctypes.c_longlong),
         ("workspace_bytes", ctypes.c_size_t),
     ]
@@ -64,6 +65,9 @@ _lib.ckl_gemm_host.argtypes = [_i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f]
 _lib.ckl_plan_gemm.argtypes = [_i, _i, _i, _i, _i, _i, _i, _i, _i, _i, ctypes.POINTER(Plan)]
 _lib.ckl_plan_sk_range.argtypes = [ctypes.POINTER(Plan), _i, ctypes.POINTER(ctypes.c_longlong),
                                    ctypes.POINTER(ctypes.c_longlong)]
+_lib.ckl_plan_unit_segments.argtypes = [ctypes.POINTER(Plan), _i, ctypes.POINTER(ctypes.c_int), _i]
+_lib.ckl_plan_fixup_slots.argtypes = [ctypes.POINTER(Plan), _i, ctypes.POINTER(ctypes.c_int), _i]
+_lib.ckl_assemble_column_blocks.argtypes = [_vp, _vp, _i, _i, _i, _i, _vp]
 _lib.ckl_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
 _lib.ckl_stream_copy.argtypes = [_vp, _vp, ctypes.c_size_t, _vp]
 _lib.ckl_last_error.restype = ctypes.c_char_p
@@ -72,7 +76,8 @@ _lib.ckl_algo_name.restype = ctypes.c_char_p
 _lib.ckl_shutdown.restype = None
 for _name in ("ckl_gemm_f16", "ckl_gemm_bf16", "ckl_gemm_ex", "ckl_gemm_bias_relu_ex",
               "ckl_bias_relu_f32", "ckl_gemm_host", "ckl_plan_gemm", "ckl_plan_sk_range",
-              "ckl_device_status", "ckl_stream_copy"):
+              "ckl_device_status", "ckl_stream_copy", "ckl_plan_unit_segments",
+              "ckl_plan_fixup_slots", "ckl_assemble_column_blocks"):
     getattr(_lib, _name).restype = ctypes.c_int
 
 
@@ -175,6 +180,32 @@ def plan_sk_range(plan: Plan, unit: int) -> tuple[int, int]:
     b, e = ctypes.c_longlong(), ctypes.c_longlong()
     _check(_lib.ckl_plan_sk_range(ctypes.byref(plan), unit, ctypes.byref(b), ctypes.byref(e)))
     return b.value, e.value
+
+
+def plan_unit_segments(plan: Plan, unit: int) -> list[tuple[int, int, int, int, int, int]]:
+    """Work list of one unit: (tile, tile_row, tile_col, kb_begin, kb_end, slot) tuples."""
+    count = _lib.ckl_plan_unit_segments(ctypes.byref(plan), unit, None, 0)
+    if count < 0:
+        raise CklError(-count, last_error())
+    buf = (ctypes.c_int * (6 * max(count, 1)))()
+    _lib.ckl_plan_unit_segments(ctypes.byref(plan), unit, buf, count)
+    return [tuple(buf[6 * i:6 * i + 6]) for i in range(count)]
+
+
+def plan_fixup_slots(plan: Plan, sk_tile: int) -> list[int]:
+    """Workspace slots the fix-up pass adds for one split tile, in order."""
+    buf = (ctypes.c_int * 512)()
+    count = _lib.ckl_plan_fixup_slots(ctypes.byref(plan), sk_tile, buf, 512)
+    if count < 0:
+        raise CklError(-count, last_error())
+    return list(buf[:count])
+
+
+def assemble_column_blocks(dst, src, elem_size: int, m: int, n_shard: int, parts: int,
+                           stream=None) -> None:
+    """[parts][m][n_shard] -> row-major [m][parts*n_shard] on the device."""
+    _check(_lib.ckl_assemble_column_blocks(_ptr(dst), _ptr(src), elem_size, m, n_shard, parts,
+                                           _stream(stream)))
 
 
 def device_status() -> list[int]:

@@ -620,6 +620,8 @@ int ckl_plan_gemm(int m, int n, int k, int lda, int ldb, int ldc, int a_align, i
     out->tiles_n = plan.sched.tiles_n;
     out->k_blocks = plan.sched.k_blocks;
     out->grid = plan.grid;
+    out->units = plan.sched.units;
+    out->group_m = plan.sched.group_m;
     out->dp_tiles = plan.sched.dp_tiles;
     out->sk_tiles = plan.sched.sk_tiles;
     out->sk_units = plan.sched.sk_tiles > 0 ? plan.sched.units : 0;
@@ -638,6 +640,94 @@ int ckl_plan_sk_range(const ckl_plan* plan, int u, long long* begin, long long* 
     s.sk_iters = plan->sk_iters;
     *begin = sk_range_begin(s, u);
     *end = sk_range_begin(s, u + 1);
+    return CKL_OK;
+}
+
+namespace {
+Schedule schedule_of(const ckl_plan* plan) {
+    Schedule s = {};
+    s.tiles_m = plan->tiles_m;
+    s.tiles_n = plan->tiles_n;
+    s.k_blocks = plan->k_blocks;
+    s.units = plan->units;
+    s.dp_tiles = plan->dp_tiles;
+    s.sk_tiles = plan->sk_tiles;
+    s.group_m = plan->group_m;
+    s.sk_iters = plan->sk_iters;
+    return s;
+}
+}  // namespace
+
+int ckl_plan_unit_segments(const ckl_plan* plan, int u, int* out, int max_segments) {
+    if (plan == nullptr || u < 0 || u >= plan->units || plan->group_m <= 0 ||
+        (out == nullptr && max_segments > 0)) {
+        fail(CKL_ERR_INVALID_ARG, "ckl_plan_unit_segments: bad plan or unit index");
+        return -CKL_ERR_INVALID_ARG;
+    }
+    const Schedule s = schedule_of(plan);
+    SegmentCursor cur = make_cursor(s, u);
+    Segment seg;
+    int count = 0;
+    while (next_segment(s, &cur, &seg)) {
+        if (count < max_segments) {
+            int tm = 0, tn = 0;
+            tile_coords(s, seg.tile, &tm, &tn);
+            int* o = out + 6 * count;
+            o[0] = seg.tile;
+            o[1] = tm;
+            o[2] = tn;
+            o[3] = seg.kb_begin;
+            o[4] = seg.kb_end;
+            o[5] = seg.slot;
+        }
+        ++count;
+    }
+    return count;
+}
+
+int ckl_plan_fixup_slots(const ckl_plan* plan, int sk_tile, int* out, int max_slots) {
+    if (plan == nullptr || sk_tile < 0 || sk_tile >= plan->sk_tiles ||
+        (out == nullptr && max_slots > 0)) {
+        fail(CKL_ERR_INVALID_ARG, "ckl_plan_fixup_slots: bad plan or tile index");
+        return -CKL_ERR_INVALID_ARG;
+    }
+    const Schedule s = schedule_of(plan);
+    int slots[kMaxFixupSlots];
+    const int count = fixup_slots(s, sk_tile, slots, kMaxFixupSlots);
+    for (int i = 0; i < count && i < max_slots; ++i) {
+        out[i] = slots[i];
+    }
+    return count;
+}
+
+int ckl_assemble_column_blocks(void* dst, const void* src, int elem_size, int m, int n_shard,
+                               int parts, ckl_stream_t stream) {
+    if (m <= 0 || n_shard <= 0 || parts <= 0) {
+        return CKL_OK;
+    }
+    if (dst == nullptr || src == nullptr || (elem_size != 2 && elem_size != 4)) {
+        return fail(CKL_ERR_INVALID_ARG,
+                    "ckl_assemble_column_blocks: null pointer or elem_size not 2 or 4");
+    }
+    const size_t row_bytes = static_cast<size_t>(n_shard) * static_cast<size_t>(elem_size);
+    const bool vec = row_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0 &&
+                     reinterpret_cast<uintptr_t>(src) % 16 == 0;
+    const size_t unit = vec ? 16 : static_cast<size_t>(elem_size);
+    const size_t per_row = row_bytes / unit;
+    const size_t total = per_row * static_cast<size_t>(m) * static_cast<size_t>(parts);
+    const int blocks = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 32));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (vec) {
+        assemble_column_blocks_kernel<uint4><<<blocks, 256, 0, s>>>(
+            static_cast<uint4*>(dst), static_cast<const uint4*>(src), per_row, m, parts);
+    } else if (elem_size == 4) {
+        assemble_column_blocks_kernel<uint32_t><<<blocks, 256, 0, s>>>(
+            static_cast<uint32_t*>(dst), static_cast<const uint32_t*>(src), per_row, m, parts);
+    } else {
+        assemble_column_blocks_kernel<uint16_t><<<blocks, 256, 0, s>>>(
+            static_cast<uint16_t*>(dst), static_cast<const uint16_t*>(src), per_row, m, parts);
+    }
+    CKL_TRY_CUDA(cudaGetLastError());
     return CKL_OK;
 }
 

@@ -163,6 +163,26 @@ __global__ void bias_relu_kernel(float* c, const float* __restrict__ bias, int m
     }
 }
 
+// [parts][m][per_row] -> [m][parts * per_row], in units of T (16-byte vectors
+// when the shard row pitch allows).  Follows the all-gather of the N-sharded
+// GEMM; pure copy, bound by HBM bandwidth (reads and writes every byte once).
+template <typename T>
+__global__ void assemble_column_blocks_kernel(T* __restrict__ dst, const T* __restrict__ src,
+                                              size_t per_row, int m, int parts) {
+    const size_t total = per_row * static_cast<size_t>(m) * static_cast<size_t>(parts);
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += stride) {
+        // i indexes dst: row r, part p, offset c inside the part's row segment
+        const size_t row_len = per_row * static_cast<size_t>(parts);
+        const size_t r = i / row_len;
+        const size_t in_row = i - r * row_len;
+        const size_t p = in_row / per_row;
+        const size_t c = in_row - p * per_row;
+        dst[i] = src[(p * static_cast<size_t>(m) + r) * per_row + c];
+    }
+}
+
 // Bandwidth probe: grid-stride 16-byte copy with four independent loads in
 // flight per thread (HBM3e needs far more bytes in flight per SM than the
 // reference's one-load-per-iteration loop, src/tools/device_probe.cu:25-31).

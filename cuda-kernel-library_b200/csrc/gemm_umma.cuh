@@ -631,34 +631,11 @@ streamk_fixup_kernel(const GemmParams p) {
     constexpr size_t kSlotFloats = static_cast<size_t>(kTileM) * kTileN;
     const Schedule& s = p.sched;
     const int sk_tile = static_cast<int>(blockIdx.x);
-    const long long it0 = static_cast<long long>(sk_tile) * s.k_blocks;
-    const long long it1 = it0 + s.k_blocks;
 
-    __shared__ int slots[512];
+    __shared__ int slots[kMaxFixupSlots];
     __shared__ int n_slots;
     if (threadIdx.x == 0) {
-        int count = 0;
-        int u = sk_owner_of(s, it0);
-        while (u < s.units) {
-            const long long b = sk_range_begin(s, u);
-            const long long e = sk_range_begin(s, u + 1);
-            if (b >= it1) {
-                break;
-            }
-            if (e > it0 && e > b) {
-                const long long lo = b > it0 ? b : it0;
-                const long long hi = e < it1 ? e : it1;
-                if (lo == it0 && hi == it1) {
-                    count = 0;  // one unit owns the whole tile: nothing to add
-                    break;
-                }
-                if (count < 512) {
-                    slots[count++] = 2 * u + (lo == it0 ? 1 : 0);
-                }
-            }
-            ++u;
-        }
-        n_slots = count;
+        n_slots = fixup_slots(s, sk_tile, slots, kMaxFixupSlots);
     }
     __syncthreads();
     const int count = n_slots;

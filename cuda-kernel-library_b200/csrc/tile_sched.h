@@ -133,4 +133,35 @@ CKL_HD int sk_owner_of(const Schedule& s, long long it) {
     return u;
 }
 
+constexpr int kMaxFixupSlots = 512;
+
+// The workspace slots holding the partial accumulators of split tile
+// `sk_tile`, in the (ascending unit) order the fix-up pass adds them.
+// Returns 0 when a single unit owned the whole tile and wrote C itself.
+CKL_HD int fixup_slots(const Schedule& s, int sk_tile, int* slots, int max_slots) {
+    const long long it0 = static_cast<long long>(sk_tile) * s.k_blocks;
+    const long long it1 = it0 + s.k_blocks;
+    int count = 0;
+    for (int u = sk_owner_of(s, it0); u < s.units; ++u) {
+        const long long b = sk_range_begin(s, u);
+        const long long e = sk_range_begin(s, u + 1);
+        if (b >= it1) {
+            break;
+        }
+        if (e <= it0 || e <= b) {
+            continue;
+        }
+        const long long lo = b > it0 ? b : it0;
+        const long long hi = e < it1 ? e : it1;
+        if (lo == it0 && hi == it1) {
+            return 0;
+        }
+        if (count < max_slots) {
+            slots[count] = 2 * u + (lo == it0 ? 1 : 0);
+        }
+        ++count;
+    }
+    return count < max_slots ? count : max_slots;
+}
+
 }  // namespace ckl

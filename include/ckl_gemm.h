@@ -109,6 +109,8 @@ typedef struct ckl_plan {
     int tile_k;         /* k elements per pipeline stage */
     int tiles_m, tiles_n, k_blocks;
     int grid;           /* CTAs launched */
+    int units;          /* schedulable workers: CTAs, or CTA pairs for the 2-CTA kernel */
+    int group_m;        /* tile rows per raster group */
     int dp_tiles;       /* tiles computed whole by one CTA (or pair) */
     int sk_tiles;       /* tiles whose k range is split across CTAs */
     int sk_units;       /* CTAs (or pairs) sharing the split tiles */
@@ -122,6 +124,19 @@ int ckl_plan_gemm(int m, int n, int k, int lda, int ldb, int ldc, int a_align, i
  * iterations [*begin, *end) of the sk_iters total.  Exposed for tests. */
 int ckl_plan_sk_range(const ckl_plan* plan, int u, long long* begin, long long* end);
 
+/* The work list of unit `u`, in execution order, produced by the very
+ * functions the kernels run.  Each segment is 6 ints: linear tile, tile row,
+ * tile column, first k block, one-past-last k block, workspace slot (-1 when
+ * the unit owns the whole tile and writes C itself).  Writes at most
+ * `max_segments` segments and returns the full count, or a negative
+ * ckl_status.  Exposed for tests. */
+int ckl_plan_unit_segments(const ckl_plan* plan, int u, int* out, int max_segments);
+
+/* The workspace slots the fix-up pass adds, in order, for split tile `sk_tile`
+ * (0 <= sk_tile < sk_tiles); 0 slots means one unit owned the tile whole.
+ * Returns the count or a negative ckl_status.  Exposed for tests. */
+int ckl_plan_fixup_slots(const ckl_plan* plan, int sk_tile, int* out, int max_slots);
+
 /* Device-side health word.  Kernels never trap or spin forever: a wait that
  * exceeds its limit records a code here and the kernel drains and exits.
  * Synchronises the current device, returns CKL_OK or CKL_ERR_DEVICE and
@@ -132,6 +147,13 @@ int ckl_device_status(unsigned int* info);
  * stream_copy in src/tools/device_probe.cu:25-70): copies `bytes` from src
  * to dst on the device with a grid sized for HBM3e. */
 int ckl_stream_copy(void* dst, const void* src, size_t bytes, ckl_stream_t stream);
+
+/* Multi-GPU helper for the N-sharded GEMM (no counterpart in the reference,
+ * which is single-GPU): after an all-gather of per-rank column blocks,
+ * src holds parts x m x n_shard elements ([rank][row][col]); this writes the
+ * row-major m x (parts * n_shard) matrix dst.  elem_size is 2 or 4 bytes. */
+int ckl_assemble_column_blocks(void* dst, const void* src, int elem_size, int m, int n_shard,
+                               int parts, ckl_stream_t stream);
 
 /* Message of the calling thread's most recent non-zero status ("" if none). */
 const char* ckl_last_error(void);

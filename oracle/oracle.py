@@ -191,6 +191,43 @@ class Reference(_Lib):
         super().__init__(_REF_PATH, "ckl_ref_")
 
 
+class RowBlockTimer:
+    """Runs the CPU GEMM on blocks of rows of one problem, B prepared once.  Uses the
+    reference's own function when oracle/_ref is built (kind "reference"), else the plain-C
+    port (kind "port").  Thread-safe: ctypes drops the GIL during the call."""
+
+    def __init__(self, b):
+        self.b = np.ascontiguousarray(b, dtype=np.float32)
+        self.k, self.n = self.b.shape
+        if have_reference():
+            self.kind = "reference"
+            self.lib = ctypes.CDLL(_REF_PATH)
+            self.lib.ckl_ref_bench_create.argtypes = [_fp, ctypes.c_int, ctypes.c_int]
+            self.lib.ckl_ref_bench_create.restype = ctypes.c_void_p
+            self.lib.ckl_ref_bench_run.argtypes = [ctypes.c_void_p, _fp, _fp, ctypes.c_int,
+                                                   ctypes.c_float, ctypes.c_float, _dp]
+            self.lib.ckl_ref_bench_run.restype = None
+            self.lib.ckl_ref_bench_destroy.argtypes = [ctypes.c_void_p]
+            self.handle = self.lib.ckl_ref_bench_create(_f(self.b), self.k, self.n)
+        else:
+            self.kind = "port"
+            self.port = Oracle()
+            self.handle = None
+
+    def run(self, a_rows, c_rows, alpha: float, beta: float, out):
+        rows = a_rows.shape[0]
+        if self.kind == "reference":
+            self.lib.ckl_ref_bench_run(self.handle, _f(a_rows), _f(c_rows), rows, alpha, beta, _d(out))
+        else:
+            self.port.lib.ckl_oracle_gemm_reference(_f(a_rows), _f(self.b), _f(c_rows), rows,
+                                                    self.n, self.k, alpha, beta, _d(out))
+
+    def close(self):
+        if self.handle is not None:
+            self.lib.ckl_ref_bench_destroy(self.handle)
+            self.handle = None
+
+
 def have_reference() -> bool:
     return os.path.exists(_REF_PATH)
 

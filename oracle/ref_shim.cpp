@@ -46,4 +46,32 @@ double ckl_ref_relative_frobenius_error(const float* actual, const double* ref, 
     return ckl::relative_frobenius_error(va, vr);
 }
 
+// Timing helper: B is converted to the std::vector the reference function takes ONCE, so a
+// timed call measures ckl::gemm_reference itself and not a 256 MB copy.  Several threads
+// may run on one handle at the same time, each on its own block of rows (B is read-only).
+struct RefBench {
+    std::vector<float> b;
+    int n;
+    int k;
+};
+
+void* ckl_ref_bench_create(const float* b, int k, int n) {
+    auto* h = new RefBench;
+    h->b.assign(b, b + static_cast<std::size_t>(k) * static_cast<std::size_t>(n));
+    h->n = n;
+    h->k = k;
+    return h;
+}
+
+void ckl_ref_bench_run(void* handle, const float* a_rows, const float* c_rows, int rows, float alpha,
+                       float beta, double* c_out) {
+    const auto* h = static_cast<const RefBench*>(handle);
+    const std::vector<float> va(a_rows, a_rows + static_cast<std::size_t>(rows) * h->k);
+    const std::vector<float> vc(c_rows, c_rows + static_cast<std::size_t>(rows) * h->n);
+    const std::vector<double> out = ckl::gemm_reference(va, h->b, vc, rows, h->n, h->k, alpha, beta);
+    std::memcpy(c_out, out.data(), out.size() * sizeof(double));
+}
+
+void ckl_ref_bench_destroy(void* handle) { delete static_cast<RefBench*>(handle); }
+
 }  // extern "C"

@@ -1,0 +1,171 @@
+"""CPU-only checks of the shipped library: it loads, exports what include/ckl_gemm.h
+declares, validates arguments, refuses to compute without a GPU, and its tile schedule
+(the same code the kernels execute) covers every (tile, k block) exactly once."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "ckl_gemm.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ckl_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(ckl):
+    lib = ctypes.CDLL(ckl.LIB_PATH)
+    names = declared_symbols()
+    assert "ckl_gemm_f16" in names and "ckl_gemm_bf16" in names and len(names) >= 15
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in ckl_gemm.h but not exported"
+
+
+def test_reference_entry_points_are_mirrored(ckl):
+    # include/ckl/gemm.hpp:68-100 of the reference: the tensor-core launchers.
+    for name in ("gemm_wmma_fp16", "gemm_wmma_bf16", "gemm_mma_ptx", "gemm_mma_ldm",
+                 "gemm_mma_opt", "gemm_mma_opt_bias", "gemm_bias_relu"):
+        assert callable(getattr(ckl, name))
+    header = open(os.path.join(ROOT, "include", "ckl", "gemm.hpp")).read()
+    for name in ("gemm_wmma_fp16", "gemm_wmma_bf16", "gemm_mma_ptx", "gemm_mma_ldm", "gemm_mma_opt",
+                 "gemm_mma_opt_bias", "gemm_bias_relu", "gemm_cublas_fp16", "gemm_cublas_bf16",
+                 "gemm_variant_name"):
+        assert re.search(rf"\b{name}\s*\(", header), name
+
+
+def test_argument_validation_needs_no_gpu(ckl):
+    # bad dtypes / algo / leading dimension are rejected before any CUDA call
+    with pytest.raises(ckl.CklError) as e:
+        ckl.gemm_ex(7, 16, 16, 16, ckl.F32, 4, 4, 4, 4, 4, 4, 1.0, 0.0)
+    assert e.value.status == ckl.ERR_INVALID_ARG
+    with pytest.raises(ckl.CklError) as e:
+        ckl.gemm_ex(ckl.F16, 16, 16, 16, 9, 4, 4, 4, 4, 4, 4, 1.0, 0.0)
+    assert e.value.status == ckl.ERR_INVALID_ARG
+    with pytest.raises(ckl.CklError) as e:
+        ckl.gemm_ex(ckl.F16, 16, 16, 16, ckl.F32, 4, 4, 4, 4, 4, 4, 1.0, 0.0, algo=99)
+    assert e.value.status == ckl.ERR_INVALID_ARG
+    with pytest.raises(ckl.CklError) as e:
+        ckl.gemm_ex(ckl.F16, 16, 16, 16, ckl.F32, 4, 8, 4, 4, 8, 4, 1.0, 0.0)  # ldc < n
+    assert e.value.status == ckl.ERR_INVALID_ARG
+    with pytest.raises(ckl.CklError) as e:
+        ckl.gemm_ex(ckl.F16, 16, 16, None, ckl.F32, 4, 4, 4, 4, 4, 4, 1.0, 0.0)  # C null
+    assert e.value.status == ckl.ERR_INVALID_ARG
+    # m <= 0 or n <= 0: nothing to do, success, pointers not looked at
+    # (reference: include/ckl/detail/wmma_gemm.cuh:145-147)
+    ckl.gemm_wmma_fp16(None, None, None, 0, 64, 64, 1.0, 0.0)
+    ckl.gemm_wmma_bf16(None, None, None, 64, 0, 128, 1.0, 0.0)
+
+
+def test_no_cpu_fallback(ckl):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present; this checks the behaviour of a machine without one")
+    with pytest.raises(ckl.CklError) as e:
+        ckl.gemm_wmma_fp16(16, 16, 16, 8, 8, 8, 1.0, 0.0)
+    assert e.value.status in (ckl.ERR_CUDA, ckl.ERR_UNSUPPORTED)
+    assert ckl.last_error()
+
+
+def test_dispatch_follows_the_reference_contract(ckl):
+    # TMA-illegal shapes go to the general kernel, like the reference's scalar fallback
+    # (include/ckl/detail/wmma_gemm.cuh:148-158); legal ones to the tensor-core kernel.
+    assert ckl.plan_gemm(129, 257, 193).algo == ckl.ALGO_SIMT      # lda=193, ldb=257
+    assert ckl.plan_gemm(7, 5, 11).algo == ckl.ALGO_SIMT
+    assert ckl.plan_gemm(256, 256, 256).algo == ckl.ALGO_UMMA_1CTA
+    assert ckl.plan_gemm(512, 384, 640).algo == ckl.ALGO_UMMA_1CTA
+    assert ckl.plan_gemm(256, 256, 256, a_align=2).algo == ckl.ALGO_SIMT
+    with pytest.raises(ckl.CklError) as e:
+        ckl.plan_gemm(129, 257, 193, algo=ckl.ALGO_UMMA_1CTA)
+    assert e.value.status == ckl.ERR_UNSUPPORTED
+    p = ckl.plan_gemm(8192, 8192, 8192)
+    assert (p.tile_m, p.tile_n, p.tile_k) == (128, 256, 64)
+    assert (p.tiles_m, p.tiles_n, p.k_blocks, p.grid) == (64, 32, 128, 148)
+    # the stream-K stress shapes split
+    for shape in [(4000, 3000, 5000), (1024, 1024, 32768)]:
+        p = ckl.plan_gemm(*shape)
+        assert p.algo == ckl.ALGO_UMMA_SK and p.sk_tiles > 0 and p.workspace_bytes > 0
+
+
+SHAPES = [(128, 256, 64), (256, 256, 256), (4000, 3000, 5000), (1024, 1024, 32768),
+          (8192, 8192, 8192), (8192, 1024, 8192), (16384, 1792, 4096), (200, 264, 72),
+          (2304, 4096, 1024), (1000, 776, 520), (128, 256, 6400), (100000, 256, 64)]
+ALGOS = ["ALGO_UMMA_1CTA", "ALGO_UMMA_SK", "ALGO_UMMA_2CTA", "ALGO_UMMA_2CTA_SK"]
+
+
+@pytest.mark.parametrize("sm_count", [148, 132, 8])
+@pytest.mark.parametrize("algo_name", ALGOS)
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_schedule_covers_every_k_block_once(ckl, shape, algo_name, sm_count):
+    m, n, k = shape
+    plan = ckl.plan_gemm(m, n, k, algo=getattr(ckl, algo_name), sm_count=sm_count)
+    tiles = plan.tiles_m * plan.tiles_n
+    assert plan.tiles_m == -(-m // plan.tile_m) and plan.tiles_n == -(-n // plan.tile_n)
+    assert plan.k_blocks == -(-k // plan.tile_k)
+    assert plan.dp_tiles + plan.sk_tiles == tiles
+    pair = plan.tile_m == 256
+    assert plan.grid == plan.units * (2 if pair else 1)
+    assert plan.units <= (sm_count // 2 if pair else sm_count)
+
+    covered = {}                      # tile -> list of (kb0, kb1, unit, slot)
+    coords = {}
+    slots_used = set()
+    per_unit_iters = []
+    for u in range(plan.units):
+        segs = ckl.plan_unit_segments(plan, u)
+        iters = 0
+        partial_positions = []
+        for idx, (tile, tm, tn, kb0, kb1, slot) in enumerate(segs):
+            assert 0 <= tile < tiles and 0 <= kb0 < kb1 <= plan.k_blocks
+            assert 0 <= tm < plan.tiles_m and 0 <= tn < plan.tiles_n
+            coords.setdefault(tile, (tm, tn))
+            assert coords[tile] == (tm, tn)
+            whole = kb0 == 0 and kb1 == plan.k_blocks
+            assert (slot == -1) == whole
+            if slot >= 0:
+                assert slot // 2 == u and slot not in slots_used
+                assert slot * plan.tile_m * plan.tile_n * 4 < plan.workspace_bytes
+                slots_used.add(slot)
+                partial_positions.append(idx)
+            covered.setdefault(tile, []).append((kb0, kb1, u, slot))
+            iters += kb1 - kb0
+        # partial accumulators only at the two ends of a unit's stream-K range
+        sk_segs = [i for i, s in enumerate(segs) if s[0] >= plan.dp_tiles]
+        for pos in partial_positions:
+            assert pos in (sk_segs[0], sk_segs[-1])
+        per_unit_iters.append(iters)
+
+    assert sorted(covered) == list(range(tiles))
+    assert len(set(coords.values())) == tiles          # the raster is a bijection
+    for tile, parts in covered.items():
+        parts.sort()
+        assert parts[0][0] == 0 and parts[-1][1] == plan.k_blocks
+        for (a0, a1, _, _), (b0, _, _, _) in zip(parts, parts[1:]):
+            assert a1 == b0
+        if tile < plan.dp_tiles:
+            assert len(parts) == 1
+    # balance: split work differs by at most one k block between units
+    if plan.sk_tiles:
+        sk = []
+        for u in range(plan.units):
+            b, e = ckl.plan_sk_range(plan, u)
+            sk.append(e - b)
+        assert sum(sk) == plan.sk_iters == plan.sk_tiles * plan.k_blocks
+        assert max(sk) - min(sk) <= 1
+    # fix-up lists name exactly the partial slots of each split tile, in unit order
+    for t in range(plan.sk_tiles):
+        expect = [slot for (_, _, _, slot) in covered[plan.dp_tiles + t] if slot >= 0]
+        assert ckl.plan_fixup_slots(plan, t) == expect
+        assert len(expect) != 1
+
+
+def test_raster_groups_keep_a_wave_compact(ckl):
+    plan = ckl.plan_gemm(8192, 8192, 8192, algo=ckl.ALGO_UMMA_1CTA)
+    first_wave = [ckl.plan_unit_segments(plan, u)[0] for u in range(plan.units)]
+    rows = {s[1] for s in first_wave}
+    cols = {s[2] for s in first_wave}
+    # 148 tiles in flight touch 16 tile rows and 10 tile columns, not a 1 x 148 strip
+    assert len(rows) == plan.group_m == 16 and len(cols) <= 10
