@@ -256,12 +256,17 @@ def run_ours(args) -> None:
     c = c_host.cuda()
     stream = torch.cuda.current_stream()
 
-    plan = ckl.plan_gemm(M, w, K, K, w, w, sm_count=torch.cuda.get_device_properties(0)
-                         .multi_processor_count)
+    algos = {ckl.algo_name(i): i for i in range(6)}
+    if args.algo not in algos:
+        raise SystemExit(f"--algo must be one of {sorted(algos)}")
+    algo = algos[args.algo]
+
+    plan = ckl.plan_gemm(M, w, K, K, w, w, algo=algos.get(args.algo, 0),
+                         sm_count=torch.cuda.get_device_properties(0).multi_processor_count)
     launches_per_step = 1 + (1 if plan.sk_tiles > 0 else 0)
 
     def step():
-        op.run(a, b, c, ALPHA, BETA, stream=stream)
+        op.run(a, b, c, ALPHA, BETA, algo=algo, stream=stream)
 
     def barrier():
         torch.cuda.synchronize()
@@ -413,6 +418,9 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--algo", default="auto",
+                    help="pin a kernel (auto, simt, umma_1cta, umma_1cta_streamk, umma_2cta, "
+                         "umma_2cta_streamk); the default is what every caller gets")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -421,7 +429,7 @@ def main() -> None:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
                f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1", "--master-port",
                str(free_port()), os.path.abspath(__file__), "--gpus", str(args.gpus), "--steps",
-               str(args.steps), "--warmup", str(args.warmup)]
+               str(args.steps), "--warmup", str(args.warmup), "--algo", args.algo]
         raise SystemExit(subprocess.call(cmd))
     run_ours(args)
 

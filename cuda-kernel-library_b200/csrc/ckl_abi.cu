@@ -7,6 +7,7 @@
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <memory>
@@ -28,6 +29,9 @@ namespace {
 using namespace ckl;
 
 thread_local std::string g_last_error;
+#ifdef CKL_EXPERIMENT
+unsigned long long* g_prof_buf = nullptr;
+#endif
 
 int fail(int code, const char* fmt, ...) {
     char buf[512];
@@ -170,7 +174,8 @@ Schedule make_schedule(int m, int n, int k, bool pair, int max_units, int want_s
     const int tile_m = pair ? 256 : 128;
     s.tiles_m = (m + tile_m - 1) / tile_m;
     s.tiles_n = (n + 255) / 256;
-    s.k_blocks = (k + 63) / 64;
+    const int tile_k = pair ? UmmaConfig<true>::kTileK : UmmaConfig<false>::kTileK;
+    s.k_blocks = (k + tile_k - 1) / tile_k;
     s.group_m = pair ? 8 : 16;
     const int tiles = s.tiles_m * s.tiles_n;
     s.units = std::max(1, std::min(max_units, tiles));
@@ -193,12 +198,10 @@ Schedule make_schedule(int m, int n, int k, bool pair, int max_units, int want_s
     }
     const long long sk_iters = static_cast<long long>(sk_tiles) * s.k_blocks;
     if (want_sk == 2) {
-        // Heuristic: split only when the last data-parallel wave would leave a
-        // noticeable part of the machine idle and the split ranges are long
-        // enough to amortise the partial-tile traffic.
-        const int waves = full_waves + 1;
-        const double dp_eff = static_cast<double>(tiles) / (static_cast<double>(waves) * max_units);
-        if (dp_eff > 0.97 || sk_iters / max_units < 8) {
+        // Heuristic (measured): the split pays for its partial-tile traffic and fix-up
+        // pass only when whole tiles would leave most of the machine idle and every unit
+        // still gets a long run of k blocks.
+        if (full_waves >= 1 || tiles * 4 > max_units || sk_iters / max_units < 8) {
             return s;
         }
     }
@@ -217,7 +220,13 @@ int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_al
     const bool legal = tma_legal(k, lda, ldb, a_align, b_align);
     int resolved = algo;
     if (algo == CKL_ALGO_AUTO) {
-        resolved = legal ? CKL_ALGO_UMMA_SK : CKL_ALGO_SIMT;
+        // Measured on B200: once there is at least one 256x256 tile per CTA pair the pair
+        // kernel wins (half the B traffic per SM); below that the 128x256 single-CTA tiles
+        // fill more SMs.
+        const long long pair_tiles =
+            static_cast<long long>((m + 255) / 256) * static_cast<long long>((n + 255) / 256);
+        const bool use_pair = max_pairs > 0 && pair_tiles >= max_pairs;
+        resolved = !legal ? CKL_ALGO_SIMT : use_pair ? CKL_ALGO_UMMA_2CTA_SK : CKL_ALGO_UMMA_SK;
     } else if (is_tensor_algo(algo) && !legal) {
         return fail(CKL_ERR_UNSUPPORTED,
                     "tensor-core algo %s needs k > 0, A and B 16-byte aligned and lda, ldb "
@@ -254,7 +263,7 @@ int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_al
     plan->pair = pair;
     plan->tile_m = pair ? 256 : 128;
     plan->tile_n = 256;
-    plan->tile_k = 64;
+    plan->tile_k = pair ? UmmaConfig<true>::kTileK : UmmaConfig<false>::kTileK;
     plan->sched = make_schedule(m, n, k, pair, max_units, want_sk);
     plan->grid = plan->sched.units * (pair ? 2 : 1);
     if (plan->sched.sk_tiles > 0) {
@@ -264,7 +273,7 @@ int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_al
     } else {
         plan->workspace_bytes = 0;
         if (algo == CKL_ALGO_AUTO) {
-            plan->algo = CKL_ALGO_UMMA_1CTA;
+            plan->algo = pair ? CKL_ALGO_UMMA_2CTA : CKL_ALGO_UMMA_1CTA;
         }
     }
     return CKL_OK;
@@ -272,14 +281,15 @@ int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_al
 
 // ---- TMA descriptors -----------------------------------------------------------
 
-int encode_2d(DeviceCtx* ctx, CUtensorMap* map, int ab_dtype, const void* base, uint64_t inner,
+int encode_2d(DeviceCtx* ctx, CUtensorMap* map, int dtype, const void* base, uint64_t inner,
               uint64_t outer, uint64_t pitch_elems, uint32_t box_inner, uint32_t box_outer) {
     const cuuint64_t dims[2] = {inner, outer};
-    const cuuint64_t strides[1] = {pitch_elems * 2ull};
+    const cuuint64_t strides[1] = {pitch_elems * dtype_size(dtype)};
     const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t elem_strides[2] = {1, 1};
-    const CUtensorMapDataType dt =
-        ab_dtype == CKL_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const CUtensorMapDataType dt = dtype == CKL_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                   : dtype == CKL_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                       : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
     const CUresult r = ctx->encode(map, dt, 2, const_cast<void*>(base), dims, strides, box,
                                    elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -315,8 +325,8 @@ int get_workspace(DeviceCtx* ctx, cudaStream_t stream, size_t bytes, float** out
 // ---- launches --------------------------------------------------------------------
 
 template <bool kPair, typename OutT>
-int launch_umma(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
-                cudaStream_t stream) {
+int launch_umma(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                const GemmParams& p, int grid, cudaStream_t stream) {
     using Cfg = UmmaConfig<kPair>;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid));
@@ -332,7 +342,7 @@ int launch_umma(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& 
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
     }
-    CKL_TRY_CUDA(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<kPair, OutT>, ta, tb, p));
+    CKL_TRY_CUDA(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<kPair, OutT>, ta, tb, tc, p));
     if (p.sched.sk_tiles > 0) {
         streamk_fixup_kernel<Cfg::kTileM, OutT><<<p.sched.sk_tiles, 256, 0, stream>>>(p);
         CKL_TRY_CUDA(cudaGetLastError());
@@ -341,10 +351,10 @@ int launch_umma(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& 
 }
 
 template <typename OutT>
-int launch_umma_out(bool pair, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
-                    int grid, cudaStream_t stream) {
-    return pair ? launch_umma<true, OutT>(ta, tb, p, grid, stream)
-                : launch_umma<false, OutT>(ta, tb, p, grid, stream);
+int launch_umma_out(bool pair, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                    const GemmParams& p, int grid, cudaStream_t stream) {
+    return pair ? launch_umma<true, OutT>(ta, tb, tc, p, grid, stream)
+                : launch_umma<false, OutT>(ta, tb, tc, p, grid, stream);
 }
 
 template <typename InT, typename OutT>
@@ -471,9 +481,35 @@ int gemm_impl(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, 
                   ? 1
                   : 0;
     p.epi_mode = epi;
+    // The coalesced epilogue moves C through TMA (32-row x 128-byte boxes); it needs the
+    // same alignment as the vector path.  Otherwise the kernel stores from registers.
+    CUtensorMap tc;
+    std::memset(&tc, 0, sizeof tc);
+    p.c_tma = p.c_vec;
+    if (p.c_tma) {
+        if (const int rc = encode_2d(ctx, &tc, c_dtype, c, static_cast<uint64_t>(n),
+                                     static_cast<uint64_t>(m), static_cast<uint64_t>(ldc),
+                                     static_cast<uint32_t>(128 / csz), 32);
+            rc != CKL_OK) {
+            return rc;
+        }
+    }
     p.idesc = ptx::make_idesc_f16(ab_dtype == CKL_F16 ? 0u : 1u, 0u, 1u, plan.pair ? 256u : 128u,
                                   256u);
     p.sched = plan.sched;
+#ifdef CKL_EXPERIMENT
+    p.debug = getenv("CKL_DEBUG") ? atoi(getenv("CKL_DEBUG")) : 0;
+    if (getenv("CKL_GROUP_M")) p.sched.group_m = atoi(getenv("CKL_GROUP_M"));
+    {
+        static unsigned long long* prof_buf = nullptr;
+        if (prof_buf == nullptr) {
+            cudaMalloc(&prof_buf, 1024 * 8 * sizeof(unsigned long long));
+        }
+        cudaMemsetAsync(prof_buf, 0, 1024 * 8 * sizeof(unsigned long long), stream);
+        p.prof = prof_buf;
+        g_prof_buf = prof_buf;
+    }
+#endif
     if (plan.workspace_bytes > 0) {
         if (const int rc = get_workspace(ctx, stream, plan.workspace_bytes, &p.workspace);
             rc != CKL_OK) {
@@ -481,9 +517,9 @@ int gemm_impl(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, 
         }
     }
     switch (c_dtype) {
-        case CKL_F32: return launch_umma_out<float>(plan.pair, ta, tb, p, plan.grid, stream);
-        case CKL_F16: return launch_umma_out<__half>(plan.pair, ta, tb, p, plan.grid, stream);
-        default: return launch_umma_out<__nv_bfloat16>(plan.pair, ta, tb, p, plan.grid, stream);
+        case CKL_F32: return launch_umma_out<float>(plan.pair, ta, tb, tc, p, plan.grid, stream);
+        case CKL_F16: return launch_umma_out<__half>(plan.pair, ta, tb, tc, p, plan.grid, stream);
+        default: return launch_umma_out<__nv_bfloat16>(plan.pair, ta, tb, tc, p, plan.grid, stream);
     }
 }
 
@@ -769,6 +805,15 @@ int ckl_stream_copy(void* dst, const void* src, size_t bytes, ckl_stream_t strea
     CKL_TRY_CUDA(cudaGetLastError());
     return CKL_OK;
 }
+
+#ifdef CKL_EXPERIMENT
+int ckl_exp_read_prof(unsigned long long* out, int ctas) {
+    cudaDeviceSynchronize();
+    return g_prof_buf ? static_cast<int>(cudaMemcpy(out, g_prof_buf, sizeof(unsigned long long) * 8 * ctas,
+                                                    cudaMemcpyDeviceToHost))
+                      : -1;
+}
+#endif
 
 const char* ckl_last_error(void) { return g_last_error.c_str(); }
 

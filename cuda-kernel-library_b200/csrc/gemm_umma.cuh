@@ -15,8 +15,8 @@
 //   kPair = true    a cluster of two CTAs per unit, output tile 256 x 256,
 //                   UMMA 256x256x16 issued by the leader CTA for both SMs
 //                   (cta_group::2).  Each CTA loads only its own 128 rows of A
-//                   and its own 128 columns of B (no multicast), 32 KB per
-//                   stage, 6 stages.
+//                   and its own 128 columns of B (no multicast); a stage holds
+//                   128 k elements (64 KB per CTA), 3 stages.
 //
 // Data layout.  A is row-major m x k, so a 128 x 64 box lands in shared memory
 // K-major: 128 rows of 128 bytes under the 128-byte swizzle.  B is row-major
@@ -61,10 +61,23 @@ struct GemmParams {
     int ldc;
     float alpha, beta;
     int c_vec;            // 16-byte vector access to C is legal
+    int c_tma;            // C can be described by a TMA tensor map (tmap_c is valid)
     int epi_mode;
     uint32_t idesc;
     Schedule sched;
+#ifdef CKL_EXPERIMENT
+    int debug;  // experiment builds only: 1 = no TMA, 2 = no MMA, 4 = no epilogue traffic
+    unsigned long long* prof;  // experiment builds only: 8 counters per CTA
+#endif
 };
+
+// Depth of the shared-memory ring (48 KB per stage for one CTA, 64 KB per CTA of a pair).
+#ifndef CKL_STAGES_1CTA
+#define CKL_STAGES_1CTA 4
+#endif
+#ifndef CKL_STAGES_2CTA
+#define CKL_STAGES_2CTA 3
+#endif
 
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
@@ -76,19 +89,28 @@ enum Role : unsigned int { kRoleProducer = 1, kRoleMma = 2, kRoleEpilogue = 3, k
 
 template <bool kPair>
 struct UmmaConfig {
-    static constexpr int kStages = kPair ? 6 : 4;
-    static constexpr int kBBoxes = kPair ? 2 : 4;  // 64-column boxes of B per CTA per stage
-    static constexpr uint32_t kABytes = 128 * 64 * 2;
+    static constexpr int kStages = kPair ? CKL_STAGES_2CTA : CKL_STAGES_1CTA;
+    static constexpr int kBBoxes = kPair ? 2 : 4;  // 64-column boxes of B per CTA per 64 k rows
+    // A stage holds kKSub sub-blocks of 64 k elements.  The CTA pair takes 128 k per stage:
+    // every tcgen05.commit that frees a stage costs the pair a cross-SM round trip, and
+    // eight MMAs per commit instead of four amortise it.
+    static constexpr int kKSub = kPair ? 2 : 1;
+    static constexpr uint32_t kASubBytes = 128 * 64 * 2;
     static constexpr uint32_t kBoxBytes = 64 * 64 * 2;
-    static constexpr uint32_t kBBytes = kBBoxes * kBoxBytes;
+    static constexpr uint32_t kBSubBytes = kBBoxes * kBoxBytes;
+    static constexpr uint32_t kABytes = kKSub * kASubBytes;
+    static constexpr uint32_t kBBytes = kKSub * kBSubBytes;
     static constexpr uint32_t kStageBytes = kABytes + kBBytes;
     static constexpr uint32_t kTxBytes = kStageBytes * (kPair ? 2 : 1);
     static constexpr int kTileM = kPair ? 256 : 128;
     static constexpr int kTileN = 256;
-    static constexpr int kTileK = 64;
-    static constexpr int kNumBarriers = 2 * kStages + 5;
-    // ring + barriers + TMEM slot + abort flag, plus slack to 1024-align the ring
-    static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kNumBarriers * 8 + 16 + 1024;
+    static constexpr int kTileK = 64 * kKSub;
+    // Epilogue staging: per epilogue warp two buffers of 32 rows x 128 B.
+    static constexpr uint32_t kStagingBytes = 4 * 2 * 4096;
+    static constexpr int kNumBarriers = 2 * kStages + 5 + 8;
+    // ring + staging + barriers + TMEM slot + abort flag, plus slack to 1024-align the ring
+    static constexpr uint32_t kSmemBytes =
+        kStages * kStageBytes + kStagingBytes + kNumBarriers * 8 + 16 + 1024;
     static constexpr int kThreads = 192;
     static constexpr size_t kSlotFloats = static_cast<size_t>(kTileM) * kTileN;
 };
@@ -293,16 +315,22 @@ __device__ __forceinline__ void finish_row_chunk(float (&acc)[32], OutT* row_ptr
 template <bool kPair, typename OutT>
 __global__ void __launch_bounds__(192, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                 const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
     using Cfg = UmmaConfig<kPair>;
     constexpr int kStages = Cfg::kStages;
+#ifdef CKL_EXPERIMENT
+    const unsigned long long prof_entry = ptx::global_timer_ns();
+#endif
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
     const uint32_t ring = (raw_addr + 1023u) & ~1023u;
     uint8_t* ring_ptr = smem_raw + (ring - raw_addr);
-    const uint32_t bars = ring + kStages * Cfg::kStageBytes;
-    uint8_t* bars_ptr = ring_ptr + kStages * Cfg::kStageBytes;
+    const uint32_t staging = ring + kStages * Cfg::kStageBytes;
+    uint8_t* staging_ptr = ring_ptr + kStages * Cfg::kStageBytes;
+    const uint32_t bars = staging + Cfg::kStagingBytes;
+    uint8_t* bars_ptr = staging_ptr + Cfg::kStagingBytes;
 
     auto full_bar = [&](int s) { return bars + 8u * static_cast<uint32_t>(s); };
     auto empty_bar = [&](int s) { return bars + 8u * static_cast<uint32_t>(kStages + s); };
@@ -311,6 +339,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         return bars + 8u * static_cast<uint32_t>(2 * kStages + 2 + a);
     };
     const uint32_t drain_bar = bars + 8u * static_cast<uint32_t>(2 * kStages + 4);
+    // C_in staging barriers: two per epilogue warp
+    auto cin_bar = [&](int w, int b) {
+        return bars + 8u * static_cast<uint32_t>(2 * kStages + 5 + 2 * w + b);
+    };
     const uint32_t tmem_slot = bars + 8u * static_cast<uint32_t>(Cfg::kNumBarriers);
     volatile uint32_t* tmem_slot_ptr =
         reinterpret_cast<volatile uint32_t*>(bars_ptr + 8 * Cfg::kNumBarriers);
@@ -339,10 +371,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ptx::mbar_init(acc_empty_bar(a), kPair ? 8 : 4);
         }
         ptx::mbar_init(drain_bar, 1);
+        for (int w = 0; w < 4; ++w) {
+            ptx::mbar_init(cin_bar(w, 0), 1);
+            ptx::mbar_init(cin_bar(w, 1), 1);
+        }
         *ctl.abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::prefetch_tensormap(&tmap_a);
         ptx::prefetch_tensormap(&tmap_b);
+        if (p.c_tma) {
+            ptx::prefetch_tensormap(&tmap_c);
+        }
     }
     if (warp == 1) {
         if constexpr (kPair) {
@@ -364,6 +403,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t tmem_base = *tmem_slot_ptr;
 
     const Schedule& sched = p.sched;
+#ifdef CKL_EXPERIMENT
+    const long long prof_c0 = clock64();
+    const unsigned long long prof_t0 = ptx::global_timer_ns();
+    long long prof_wait = 0, prof_wait2 = 0;
+#define CKL_PROF_BEGIN() const long long prof_b_ = clock64()
+#define CKL_PROF_END(acc_) acc_ += clock64() - prof_b_
+#else
+#define CKL_PROF_BEGIN()
+#define CKL_PROF_END(acc_)
+#endif
 
     // ---- roles ----------------------------------------------------------------
     if (warp == 0) {
@@ -371,7 +420,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // TMA producer.
             SegmentCursor cur = make_cursor(sched, unit);
             Segment seg;
-            uint32_t it = 0;
+            uint32_t it = 0;       // k blocks issued so far
+            int stage = 0;         // it % kStages
+            uint32_t phase = 0;    // (it / kStages) & 1
             bool ok = true;
             while (ok && next_segment(sched, &cur, &seg)) {
                 int tm, tn;
@@ -379,36 +430,60 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 const int a_row = tm * Cfg::kTileM + (kPair ? static_cast<int>(rank) * 128 : 0);
                 const int b_col = tn * Cfg::kTileN + (kPair ? static_cast<int>(rank) * 128 : 0);
                 for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb) {
-                    const int s = static_cast<int>(it % kStages);
-                    const uint32_t use = it / kStages;
-                    if (!detail::wait_barrier(empty_bar(s), (use & 1u) ^ 1u, ctl, kRoleProducer,
-                                              it)) {
-                        ok = false;
-                        break;
+                    {
+                        CKL_PROF_BEGIN();
+                        const bool got = detail::wait_barrier(empty_bar(stage), phase ^ 1u, ctl,
+                                                              kRoleProducer, it);
+                        CKL_PROF_END(prof_wait);
+                        if (!got) {
+                            ok = false;
+                            break;
+                        }
                     }
-                    const uint32_t a_dst = ring + static_cast<uint32_t>(s) * Cfg::kStageBytes;
+                    const uint32_t a_dst = ring + static_cast<uint32_t>(stage) * Cfg::kStageBytes;
                     const uint32_t b_dst = a_dst + Cfg::kABytes;
-                    if constexpr (kPair) {
-                        if (leader) {
-                            ptx::mbar_arrive_expect_tx(full_bar(s), Cfg::kTxBytes);
+#ifdef CKL_EXPERIMENT
+                    if (p.debug & 1) {
+                        if (!kPair || leader) ptx::mbar_arrive(full_bar(stage));
+                    } else
+#endif
+                    {
+                        uint32_t bar = full_bar(stage);
+                        if constexpr (kPair) {
+                            if (leader) {
+                                ptx::mbar_arrive_expect_tx(bar, Cfg::kTxBytes);
+                            }
+                            bar = ptx::map_to_cta(bar, 0);  // both CTAs credit the leader's barrier
+                        } else {
+                            ptx::mbar_arrive_expect_tx(bar, Cfg::kTxBytes);
                         }
-                        const uint32_t bar = ptx::map_to_cta(full_bar(s), 0);
-                        ptx::tma_load_2d_pair(a_dst, &tmap_a, bar, kb * 64, a_row);
 #pragma unroll
-                        for (int j = 0; j < Cfg::kBBoxes; ++j) {
-                            ptx::tma_load_2d_pair(b_dst + j * Cfg::kBoxBytes, &tmap_b, bar,
-                                                  b_col + j * 64, kb * 64);
-                        }
-                    } else {
-                        ptx::mbar_arrive_expect_tx(full_bar(s), Cfg::kTxBytes);
-                        ptx::tma_load_2d(a_dst, &tmap_a, full_bar(s), kb * 64, a_row);
+                        for (int sub = 0; sub < Cfg::kKSub; ++sub) {
+                            const int k0 = kb * Cfg::kTileK + sub * 64;
+                            const uint32_t a_sub = a_dst + sub * Cfg::kASubBytes;
+                            const uint32_t b_sub = b_dst + sub * Cfg::kBSubBytes;
+                            if constexpr (kPair) {
+                                ptx::tma_load_2d_pair(a_sub, &tmap_a, bar, k0, a_row);
+                            } else {
+                                ptx::tma_load_2d(a_sub, &tmap_a, bar, k0, a_row);
+                            }
 #pragma unroll
-                        for (int j = 0; j < Cfg::kBBoxes; ++j) {
-                            ptx::tma_load_2d(b_dst + j * Cfg::kBoxBytes, &tmap_b, full_bar(s),
-                                             b_col + j * 64, kb * 64);
+                            for (int j = 0; j < Cfg::kBBoxes; ++j) {
+                                if constexpr (kPair) {
+                                    ptx::tma_load_2d_pair(b_sub + j * Cfg::kBoxBytes, &tmap_b, bar,
+                                                          b_col + j * 64, k0);
+                                } else {
+                                    ptx::tma_load_2d(b_sub + j * Cfg::kBoxBytes, &tmap_b, bar,
+                                                     b_col + j * 64, k0);
+                                }
+                            }
                         }
                     }
                     ++it;
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
                 }
             }
             // Tail: do not leave while the consumer may still signal this CTA's
@@ -438,65 +513,128 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             SegmentCursor cur = make_cursor(sched, unit);
             Segment seg;
             uint32_t it = 0;
+            int stage = 0;
+            uint32_t phase = 0;
             uint32_t seg_count = 0;
             bool ok = true;
             while (ok && next_segment(sched, &cur, &seg)) {
                 const uint32_t acc = seg_count & 1u;
                 const uint32_t acc_use = seg_count >> 1;
-                if (!detail::wait_barrier(acc_empty_bar(acc), (acc_use & 1u) ^ 1u, ctl, kRoleMma,
-                                          0x80000000u | seg_count)) {
-                    ok = false;
-                    break;
-                }
-                ptx::tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + acc * 256u;
-                for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb) {
-                    const int s = static_cast<int>(it % kStages);
-                    const uint32_t use = it / kStages;
-                    if (!detail::wait_barrier(full_bar(s), use & 1u, ctl, kRoleMma, it)) {
+                {
+                    CKL_PROF_BEGIN();
+                    const bool got = detail::wait_barrier(acc_empty_bar(acc), (acc_use & 1u) ^ 1u,
+                                                          ctl, kRoleMma, 0x80000000u | seg_count);
+                    CKL_PROF_END(prof_wait2);
+                    if (!got) {
                         ok = false;
                         break;
                     }
-                    ptx::tc_fence_after_sync();
-                    const uint32_t a_src = ring + static_cast<uint32_t>(s) * Cfg::kStageBytes;
+                }
+                ptx::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * 256u;
+                // The barrier of the NEXT stage is probed between the MMAs of the current
+                // one, so that its latency hides behind tensor-core work and the next
+                // k block can be issued back to back.
+                bool ready = false;
+                for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb) {
+                    if (!ready) {
+                        CKL_PROF_BEGIN();
+                        const bool got = detail::wait_barrier(full_bar(stage), phase, ctl, kRoleMma, it);
+                        CKL_PROF_END(prof_wait);
+                        if (!got) {
+                            ok = false;
+                            break;
+                        }
+                    }
+                    const uint32_t a_src = ring + static_cast<uint32_t>(stage) * Cfg::kStageBytes;
                     const uint32_t b_src = a_src + Cfg::kABytes;
                     // A: K-major, 8-row groups 1024 B apart.  B: N-major, 64-column
                     // boxes 8192 B apart (leading), 8-k-row groups 1024 B apart (stride).
                     const uint64_t a_desc = ptx::make_smem_desc_sw128(a_src, 16, 1024);
                     const uint64_t b_desc = ptx::make_smem_desc_sw128(b_src, Cfg::kBoxBytes, 1024);
+                    int next_stage = stage + 1;
+                    uint32_t next_phase = phase;
+                    if (next_stage == kStages) {
+                        next_stage = 0;
+                        next_phase ^= 1u;
+                    }
+#ifdef CKL_EXPERIMENT
+                    if (p.debug & 2) {
+                        ptx::mbar_arrive(empty_bar(stage));
+                        if (kPair) ptx::mbar_arrive_cluster(ptx::map_to_cta(empty_bar(stage), 1));
+                        ++it;
+                        stage = next_stage;
+                        phase = next_phase;
+                        continue;
+                    }
+#endif
+                    ready = false;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
+                    for (int j = 0; j < 4 * Cfg::kKSub; ++j) {
                         // 16 k elements per instruction: +32 B along a K-major row of A,
-                        // +16 k-rows (2048 B) of B.  Descriptor addresses count 16 B.
+                        // +16 k-rows (2048 B) of B; descriptor addresses count 16 B.  Every
+                        // fourth instruction moves on to the next 64-k sub-block of the stage.
+                        const uint64_t a_off = static_cast<uint64_t>(
+                            ((j >> 2) * Cfg::kASubBytes + (j & 3) * 32) >> 4);
+                        const uint64_t b_off = static_cast<uint64_t>(
+                            ((j >> 2) * Cfg::kBSubBytes + (j & 3) * 2048) >> 4);
                         const uint32_t accumulate = (kb > seg.kb_begin || j > 0) ? 1u : 0u;
                         if constexpr (kPair) {
-                            ptx::umma_f16_pair(d_tmem, a_desc + static_cast<uint64_t>(j * 2),
-                                               b_desc + static_cast<uint64_t>(j * 128), p.idesc,
+                            ptx::umma_f16_pair(d_tmem, a_desc + a_off, b_desc + b_off, p.idesc,
                                                accumulate);
                         } else {
-                            ptx::umma_f16(d_tmem, a_desc + static_cast<uint64_t>(j * 2),
-                                          b_desc + static_cast<uint64_t>(j * 128), p.idesc,
+                            ptx::umma_f16(d_tmem, a_desc + a_off, b_desc + b_off, p.idesc,
                                           accumulate);
+                        }
+                        if (j == 0 && kb + 1 < seg.kb_end) {
+                            ready = ptx::mbar_try_wait(full_bar(next_stage), next_phase);
                         }
                     }
                     if constexpr (kPair) {
-                        ptx::umma_commit_pair(empty_bar(s));
-                        ptx::umma_commit_pair(ptx::map_to_cta(empty_bar(s), 1));
+#ifdef CKL_PAIR_MCAST_COMMIT
+                        ptx::umma_commit_pair_both(empty_bar(stage));
+#else
+                        ptx::umma_commit_pair(empty_bar(stage));
+                        ptx::umma_commit_pair(ptx::map_to_cta(empty_bar(stage), 1));
+#endif
                     } else {
-                        ptx::umma_commit(empty_bar(s));
+                        ptx::umma_commit(empty_bar(stage));
                     }
                     ++it;
+                    stage = next_stage;
+                    phase = next_phase;
                 }
+#ifdef CKL_EXPERIMENT
+                if (ok && (p.debug & 2)) {
+                    ptx::mbar_arrive(acc_full_bar(acc));
+                    if (kPair) ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_full_bar(acc), 1));
+                    ++seg_count;
+                    continue;
+                }
+#endif
                 if (ok) {
                     if constexpr (kPair) {
+#ifdef CKL_PAIR_MCAST_COMMIT
+                        ptx::umma_commit_pair_both(acc_full_bar(acc));
+#else
                         ptx::umma_commit_pair(acc_full_bar(acc));
                         ptx::umma_commit_pair(ptx::map_to_cta(acc_full_bar(acc), 1));
+#endif
                     } else {
                         ptx::umma_commit(acc_full_bar(acc));
                     }
                     ++seg_count;
                 }
             }
+#ifdef CKL_EXPERIMENT
+            if (p.prof) {
+                p.prof[blockIdx.x * 8 + 0] = static_cast<unsigned long long>(clock64() - prof_c0);
+                p.prof[blockIdx.x * 8 + 1] = ptx::global_timer_ns();   // MMA loop done (absolute)
+                p.prof[blockIdx.x * 8 + 4] = static_cast<unsigned long long>(prof_wait);
+                p.prof[blockIdx.x * 8 + 5] = static_cast<unsigned long long>(prof_wait2);
+                p.prof[blockIdx.x * 8 + 6] = it;
+            }
+#endif
             if (ok) {
                 // Tail: the epilogue (of both CTAs) must have drained the last
                 // accumulators before TMEM can go.
@@ -518,14 +656,44 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     } else {
         // Epilogue warps 2..5; TMEM lane quarter = warp id mod 4.
         const uint32_t quad = static_cast<uint32_t>(warp) & 3u;
+        const int ew = warp - 2;  // staging slice of this warp
         SegmentCursor cur = make_cursor(sched, unit);
         Segment seg;
         uint32_t seg_count = 0;
         OutT* c_base = static_cast<OutT*>(p.c);
         const bool vec_ok = p.c_vec != 0;
-        while (next_segment(sched, &cur, &seg)) {
+        // TMA epilogue state: two 4 KB staging buffers (32 rows x 128 B, 128-byte
+        // swizzle), one C_in barrier each; bit b of cin_parity = next phase to wait for.
+        constexpr int kChunkCols = 128 / static_cast<int>(sizeof(OutT));
+        constexpr int kChunks = Cfg::kTileN / kChunkCols;
+        constexpr int kUnitElems = 16 / static_cast<int>(sizeof(OutT));
+        const uint32_t stg = staging + static_cast<uint32_t>(ew) * 8192u;
+        uint8_t* stg_ptr = staging_ptr + ew * 8192;
+        uint32_t cin_parity = 0;
+        uint32_t cin_pending = 0;  // lane 0: loads issued and not yet waited for
+        const bool reads_c = (p.epi_mode == kEpiLinear) && (p.beta != 0.0f);
+        bool alive = true;
+        while (alive && next_segment(sched, &cur, &seg)) {
             const uint32_t acc = seg_count & 1u;
             const uint32_t acc_use = seg_count >> 1;
+            int tm, tn;
+            tile_coords(sched, seg.tile, &tm, &tn);
+            const int row_in_tile = (kPair ? static_cast<int>(rank) * 128 : 0) +
+                                    static_cast<int>(quad) * 32 + static_cast<int>(lane);
+            const int row = tm * Cfg::kTileM + row_in_tile;
+            const int row0 = row - static_cast<int>(lane);  // first row of this warp
+            const int col_base = tn * Cfg::kTileN;
+            const uint32_t t_row = tmem_base + ((quad * 32u) << 16) + acc * 256u;
+            const bool tma_path = (p.c_tma != 0) && seg.slot < 0;
+            const bool warp_has_rows = row0 < p.m;
+
+            // C_in of the first chunk can be fetched before the accumulator is ready.
+            if (tma_path && reads_c && warp_has_rows && lane == 0) {
+                ptx::mbar_arrive_expect_tx(cin_bar(ew, 0), 4096);
+                ptx::tma_load_2d(stg, &tmap_c, cin_bar(ew, 0), col_base, row0);
+                cin_pending |= 1u;
+            }
+
             int ok = 1;
             if (lane == 0) {
                 ok = detail::wait_barrier(acc_full_bar(acc), acc_use & 1u, ctl, kRoleEpilogue,
@@ -543,14 +711,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
             ptx::tc_fence_after_sync();
 
-            int tm, tn;
-            tile_coords(sched, seg.tile, &tm, &tn);
-            const int row_in_tile = (kPair ? static_cast<int>(rank) * 128 : 0) +
-                                    static_cast<int>(quad) * 32 + static_cast<int>(lane);
-            const int row = tm * Cfg::kTileM + row_in_tile;
-            const int col_base = tn * Cfg::kTileN;
-            const uint32_t t_row = tmem_base + ((quad * 32u) << 16) + acc * 256u;
-
+#ifdef CKL_EXPERIMENT
+            if (p.debug & 4) {
+            } else
+#endif
             if (seg.slot >= 0) {
                 // Partial accumulator -> FP32 workspace slot, full tile, no predication.
                 float* dst = p.workspace + static_cast<size_t>(seg.slot) * Cfg::kSlotFloats +
@@ -564,6 +728,102 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     for (int q = 0; q < 8; ++q) {
                         *reinterpret_cast<uint4*>(dst + c * 32 + q * 4) =
                             make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                    }
+                }
+            } else if (tma_path) {
+                // Coalesced path: registers -> swizzled staging -> TMA store (and C_in
+                // arrives by TMA load into the same buffer, one chunk ahead).
+                if (warp_has_rows) {
+#pragma unroll 1
+                    for (int c = 0; c < kChunks; ++c) {
+                        const int col = col_base + c * kChunkCols;
+                        if (col >= p.n) {
+                            break;  // uniform
+                        }
+                        const uint32_t b = static_cast<uint32_t>(c) & 1u;
+                        const bool next_chunk = (c + 1 < kChunks) && (col + kChunkCols < p.n);
+                        if (reads_c) {
+                            if (next_chunk && lane == 0) {
+                                // buffer b^1 was the source of the previous chunk's store
+                                ptx::bulk_wait_group_read<0>();
+                                ptx::mbar_arrive_expect_tx(cin_bar(ew, b ^ 1u), 4096);
+                                ptx::tma_load_2d(stg + (b ^ 1u) * 4096u, &tmap_c, cin_bar(ew, b ^ 1u),
+                                                 col + kChunkCols, row0);
+                                cin_pending |= 1u << (b ^ 1u);
+                            }
+                        } else {
+                            // buffer b was the source of the store two chunks ago
+                            if (lane == 0) {
+                                ptx::bulk_wait_group_read<1>();
+                            }
+                            __syncwarp();
+                        }
+                        float acc_f[kChunkCols];
+#pragma unroll
+                        for (int h = 0; h < kChunkCols / 32; ++h) {
+                            uint32_t r[32];
+                            ptx::tmem_ld_32x32(
+                                t_row + static_cast<uint32_t>(c * kChunkCols + h * 32), r);
+                            ptx::tmem_ld_wait();
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) {
+                                acc_f[h * 32 + e] = __uint_as_float(r[e]);
+                            }
+                        }
+                        if (reads_c) {
+                            int got = 1;
+                            if (lane == 0) {
+                                got = detail::wait_barrier(cin_bar(ew, b), (cin_parity >> b) & 1u,
+                                                           ctl, kRoleEpilogue, 0x40000000u | seg_count)
+                                          ? 1
+                                          : 0;
+                                cin_pending &= ~(1u << b);
+                            }
+                            got = __shfl_sync(0xFFFFFFFFu, got, 0);
+                            if (!got) {
+                                alive = false;
+                                break;
+                            }
+                            for (int i = 0;
+                                 i < 1024 && !ptx::mbar_try_wait(cin_bar(ew, b), (cin_parity >> b) & 1u);
+                                 ++i) {
+                            }
+                            cin_parity ^= 1u << b;
+                        }
+                        uint8_t* row_smem = stg_ptr + b * 4096u + lane * 128u;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            OutT* unit_ptr = reinterpret_cast<OutT*>(
+                                row_smem + ((static_cast<uint32_t>(j) ^ (lane & 7u)) << 4));
+                            float out[kUnitElems];
+                            if (p.epi_mode == kEpiBiasRelu) {
+#pragma unroll
+                                for (int e = 0; e < kUnitElems; ++e) {
+                                    const int gc = col + j * kUnitElems + e;
+                                    const float bv = gc < p.n ? __ldg(p.bias + gc) : 0.0f;
+                                    out[e] = fmaxf(p.alpha * acc_f[j * kUnitElems + e] + bv, 0.0f);
+                                }
+                            } else if (reads_c) {
+                                float cin[kUnitElems];
+                                detail::OutTraits<OutT>::load_vec(unit_ptr, cin);
+#pragma unroll
+                                for (int e = 0; e < kUnitElems; ++e) {
+                                    out[e] = p.alpha * acc_f[j * kUnitElems + e] + p.beta * cin[e];
+                                }
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < kUnitElems; ++e) {
+                                    out[e] = p.alpha * acc_f[j * kUnitElems + e];
+                                }
+                            }
+                            detail::OutTraits<OutT>::store_vec(unit_ptr, out);
+                        }
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            ptx::tma_store_2d(&tmap_c, stg + b * 4096u, col, row0);
+                            ptx::bulk_commit_group();
+                        }
                     }
                 }
             } else {
@@ -588,6 +848,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     }
                 }
             }
+            // All TMEM reads of this accumulator are done: hand it back to the MMA warp.
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) {
@@ -596,8 +857,21 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 } else {
                     ptx::mbar_arrive(acc_empty_bar(acc));
                 }
+                if (tma_path) {
+                    ptx::bulk_wait_group_read<0>();  // staging is reusable by the next tile
+                }
             }
+            __syncwarp();
             ++seg_count;
+        }
+        if (lane == 0) {
+            // Leaving: no store may still read staging, no C_in copy may still write it.
+            ptx::bulk_wait_group_read<0>();
+            for (uint32_t b = 0; b < 2; ++b) {
+                if (cin_pending & (1u << b)) {
+                    detail::drain_wait(cin_bar(ew, static_cast<int>(b)), (cin_parity >> b) & 1u);
+                }
+            }
         }
     }
 
@@ -618,6 +892,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ptx::tmem_dealloc(tmem_base, 512);
         }
     }
+#ifdef CKL_EXPERIMENT
+    if (p.prof && threadIdx.x == 0) {
+        p.prof[blockIdx.x * 8 + 7] = ptx::global_timer_ns();  // exit (absolute)
+        p.prof[blockIdx.x * 8 + 2] = prof_entry;              // entry (absolute)
+        p.prof[blockIdx.x * 8 + 3] = prof_t0;                 // set-up done (absolute)
+    }
+#endif
 }
 
 // Fix-up pass of the stream-K split: one CTA per split tile.  Adds the FP32

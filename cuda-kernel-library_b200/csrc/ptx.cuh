@@ -128,6 +128,26 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtens
         : "memory");
 }
 
+// 2-D tiled store, this CTA's shared memory -> global, tracked by the thread's
+// bulk async-group (commit, then wait_group.read before reusing the source).
+// Coordinates outside the tensor are clipped; x obeys the same 16-byte rule.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t smem_src, int32_t x,
+                                             int32_t y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 :
+                 : "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_src), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Waits until at most N of this thread's committed bulk groups still READ their
+// shared-memory source (the global writes may still be in flight).
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
 // ---- tensor memory ----------------------------------------------------------
 
 // Whole-warp: allocate `cols` (power of two >= 32) TMEM columns; the base
@@ -209,6 +229,19 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
                      cluster_bar)
                  : "memory");
 }
+
+#ifdef CKL_PAIR_MCAST_COMMIT
+// Pair form signalling the barrier at the same offset in both CTAs of the pair.
+__device__ __forceinline__ void umma_commit_pair_both(uint32_t bar) {
+    asm volatile(
+        "{\n\t"
+        ".reg .b16 m;\n\t"
+        "mov.b16 m, 3;\n\t"
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t"
+        "}" ::"r"(bar)
+        : "memory");
+}
+#endif
 
 // ---- tcgen05.ld -------------------------------------------------------------
 

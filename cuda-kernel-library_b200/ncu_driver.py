@@ -1,0 +1,68 @@
+"""Launch one GEMM configuration a few times so Nsight Compute can capture it.
+
+Counterpart of the reference's benchmarks/ncu_driver.cpp:41-97 (run one variant N times and
+let `ncu --launch-skip` pick a warm launch).  Example, the capture behind the summaries in
+profiles/:
+
+    ncu --set full --clock-control none -k regex:umma_gemm_kernel -s 2 -c 1 -o gpurun_out/prof \
+        python cuda-kernel-library_b200/ncu_driver.py --m 8192 --n 8192 --k 8192 \
+        --in bf16 --out bf16 --beta 0.5 --algo umma_1cta --iters 4
+
+Prints the CUDA-event time of the last launch (never quote a time taken under ncu).
+"""
+
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import os
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--in", dest="in_dtype", choices=["f16", "bf16"], default="bf16")
+    ap.add_argument("--out", dest="out_dtype", choices=["f32", "f16", "bf16"], default="bf16")
+    ap.add_argument("--alpha", type=float, default=1.0)
+    ap.add_argument("--beta", type=float, default=0.0)
+    ap.add_argument("--algo", default="auto")
+    ap.add_argument("--iters", type=int, default=4)
+    args = ap.parse_args()
+
+    import torch
+    spec = importlib.util.spec_from_file_location("ckl_b200", os.path.join(HERE, "__init__.py"),
+                                                  submodule_search_locations=[HERE])
+    ckl = importlib.util.module_from_spec(spec)
+    sys.modules["ckl_b200"] = ckl
+    spec.loader.exec_module(ckl)
+
+    algos = {ckl.algo_name(i): i for i in range(6)}
+    if args.algo not in algos:
+        raise SystemExit(f"--algo must be one of {sorted(algos)}")
+    tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
+    cdt = {"f16": ckl.F16, "bf16": ckl.BF16, "f32": ckl.F32}
+    m, n, k = args.m, args.n, args.k
+    g = torch.Generator(device="cuda").manual_seed(7)
+    a = (torch.randn(m, k, device="cuda", generator=g) * 0.02).to(tdt[args.in_dtype])
+    b = (torch.randn(k, n, device="cuda", generator=g) * 0.02).to(tdt[args.in_dtype])
+    c = (torch.randn(m, n, device="cuda", generator=g) * 0.02).to(tdt[args.out_dtype])
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(args.iters):
+        e0.record()
+        ckl.gemm_ex(cdt[args.in_dtype], a, b, c, cdt[args.out_dtype], m, n, k, k, n, n, args.alpha,
+                    args.beta, algos[args.algo])
+        e1.record()
+    torch.cuda.synchronize()
+    ckl.device_status()
+    ms = e0.elapsed_time(e1)
+    print(f"{args.algo} {m}x{n}x{k} in={args.in_dtype} out={args.out_dtype} beta={args.beta}: "
+          f"{ms:.4f} ms, {2.0 * m * n * k / ms / 1e9:.1f} TFLOP/s (last of {args.iters} launches)")
+
+
+if __name__ == "__main__":
+    main()

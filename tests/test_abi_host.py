@@ -81,13 +81,20 @@ def test_dispatch_follows_the_reference_contract(ckl):
     with pytest.raises(ckl.CklError) as e:
         ckl.plan_gemm(129, 257, 193, algo=ckl.ALGO_UMMA_1CTA)
     assert e.value.status == ckl.ERR_UNSUPPORTED
+    # large problems: CTA pairs, 256x256 tile, 128 k per stage
     p = ckl.plan_gemm(8192, 8192, 8192)
+    assert p.algo == ckl.ALGO_UMMA_2CTA
+    assert (p.tile_m, p.tile_n, p.tile_k) == (256, 256, 128)
+    assert (p.tiles_m, p.tiles_n, p.k_blocks, p.grid, p.units) == (32, 32, 64, 148, 74)
+    p = ckl.plan_gemm(8192, 8192, 8192, algo=ckl.ALGO_UMMA_1CTA)
     assert (p.tile_m, p.tile_n, p.tile_k) == (128, 256, 64)
     assert (p.tiles_m, p.tiles_n, p.k_blocks, p.grid) == (64, 32, 128, 148)
-    # the stream-K stress shapes split
-    for shape in [(4000, 3000, 5000), (1024, 1024, 32768)]:
-        p = ckl.plan_gemm(*shape)
-        assert p.algo == ckl.ALGO_UMMA_SK and p.sk_tiles > 0 and p.workspace_bytes > 0
+    # the skinny stream-K stress shape splits by default; forcing the split works anywhere
+    p = ckl.plan_gemm(1024, 1024, 32768)
+    assert p.algo == ckl.ALGO_UMMA_SK and p.sk_tiles == 32 and p.workspace_bytes > 0
+    for algo in (ckl.ALGO_UMMA_SK, ckl.ALGO_UMMA_2CTA_SK):
+        p = ckl.plan_gemm(4000, 3000, 5000, algo=algo)
+        assert p.sk_tiles > 0 and p.workspace_bytes > 0
 
 
 SHAPES = [(128, 256, 64), (256, 256, 256), (4000, 3000, 5000), (1024, 1024, 32768),

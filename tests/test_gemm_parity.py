@@ -337,14 +337,18 @@ def test_config_bf16_8192_cubed_beta(env):
     _run_large(env, 8192, 8192, 8192, env.ckl.BF16, env.ckl.BF16, 1.0, 0.5, "normal002", 8, 8)
 
 
-def test_config_bf16_8192_cubed_pair_kernel(env):
+def test_config_bf16_8192_cubed_single_cta_kernel(env):
     _run_large(env, 8192, 8192, 8192, env.ckl.BF16, env.ckl.F32, 1.0, 0.0, "normal002", 6, 6,
-               algo=env.ckl.ALGO_UMMA_2CTA_SK)
+               algo=env.ckl.ALGO_UMMA_SK)
 
 
-def test_config_streamk_ragged(env):
-    assert env.ckl.plan_gemm(4000, 3000, 5000).sk_tiles > 0
-    _run_large(env, 4000, 3000, 5000, env.ckl.F16, env.ckl.F16, 1.0, 0.0, "uniform", 12, 12)
+@pytest.mark.parametrize("algo_name", ["ALGO_AUTO", "ALGO_UMMA_SK", "ALGO_UMMA_2CTA_SK"])
+def test_config_streamk_ragged(env, algo_name):
+    algo = getattr(env.ckl, algo_name)
+    if algo != env.ckl.ALGO_AUTO:
+        assert env.ckl.plan_gemm(4000, 3000, 5000, algo=algo).sk_tiles > 0
+    _run_large(env, 4000, 3000, 5000, env.ckl.F16, env.ckl.F16, 1.0, 0.0, "uniform", 12, 12,
+               algo=algo)
 
 
 def test_config_streamk_skinny(env):
