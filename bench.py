@@ -44,8 +44,8 @@ DATASHEET_DENSE_BF16_TFLOPS = 2250.0
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0}
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the
-# ncu capture summarised under profiles/ (null until a capture of that workload exists).
-NCU_DRAM_TRAFFIC_BYTES = {"bf16_8192_cubed": None}
+# ncu capture summarised in profiles/umma_gemm_kernel_pair_bf16_8192_cubed.md (1 GPU, whole problem).
+NCU_DRAM_TRAFFIC_BYTES = {"bf16_8192_cubed": 1_367_472_904}  # 1.238 GB read + 0.129 GB written
 
 
 def load_module(name: str, path: str, search=None):
