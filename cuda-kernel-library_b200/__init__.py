@@ -220,5 +220,26 @@ def stream_copy(dst, src, nbytes: int, stream=None) -> None:
     _check(_lib.ckl_stream_copy(_ptr(dst), _ptr(src), nbytes, _stream(stream)))
 
 
+_lib.ckl_gemm_streamk_noalloc.argtypes = [_i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]
+_lib.ckl_gemm_streamk_noalloc.restype = ctypes.c_int
+_lib.ckl_noalloc_last_error.restype = ctypes.c_char_p
+_lib.ckl_noalloc_scratch_bytes.restype = ctypes.c_size_t
+
+
+def gemm_streamk_noalloc(ab_dtype, a, b, c, c_dtype, m, n, k, lda, ldb, ldc, alpha, beta,
+                         stream=None) -> None:
+    """Stream-K GEMM that never allocates device memory (built-in scratch); for hosts that own
+    all device memory themselves or cannot afford cudaMalloc's synchronisation.  One call at a
+    time per device; make the first call before any stream capture."""
+    status = _lib.ckl_gemm_streamk_noalloc(ab_dtype, _ptr(a), _ptr(b), _ptr(c), c_dtype, m, n, k,
+                                           lda, ldb, ldc, alpha, beta, _stream(stream))
+    if status != OK:
+        raise CklError(status, _lib.ckl_noalloc_last_error().decode())
+
+
+def noalloc_scratch_bytes() -> int:
+    return int(_lib.ckl_noalloc_scratch_bytes())
+
+
 def shutdown() -> None:
     _lib.ckl_shutdown()

@@ -155,6 +155,34 @@ int ckl_stream_copy(void* dst, const void* src, size_t bytes, ckl_stream_t strea
 int ckl_assemble_column_blocks(void* dst, const void* src, int elem_size, int m, int n_shard,
                                int parts, ckl_stream_t stream);
 
+/* No counterpart in the reference.  The stream-K tensor-core GEMM for callers that
+ * must not allocate device memory: hosts that have given all device memory to an
+ * arena of their own (a cudaMalloc inside a library would fail or break their
+ * budget) and latency-critical loops that cannot take cudaMalloc's device-wide
+ * synchronisation.  Same arguments and result as ckl_gemm_ex with
+ * CKL_ALGO_UMMA_SK, but the partial-tile workspace and the status word are arrays
+ * built into the library image (ckl_noalloc_scratch_bytes() = 38,797,312 bytes,
+ * held by every GPU that loads the library until the process exits) and no
+ * cudaMalloc, cudaFree or allocating routine is ever called.
+ *   - Only the tensor-core kernel: A and B 16-byte aligned, lda and ldb multiples
+ *     of 8, k > 0; anything else returns CKL_ERR_UNSUPPORTED (m <= 0 or n <= 0 is
+ *     still a no-op).
+ *   - The scratch serves schedules of up to 148 CTAs; a device that would need
+ *     more returns CKL_ERR_TOO_LARGE.
+ *   - All calls on a device share the scratch, which keeps the previous call's
+ *     contents (harmless: every slot is rewritten before it is read).  Calls
+ *     that overlap on the GPU race on it: use one stream per device or order
+ *     them with events.
+ *   - The first call on each device does one-time set-up with that device
+ *     current (symbol address look-ups, kernel attributes, driver entry point);
+ *     make it before any stream capture starts.
+ * Errors of this entry point are described by ckl_noalloc_last_error(). */
+int ckl_gemm_streamk_noalloc(int ab_dtype, const void* a, const void* b, void* c, int c_dtype,
+                             int m, int n, int k, int lda, int ldb, int ldc, float alpha,
+                             float beta, ckl_stream_t stream);
+const char* ckl_noalloc_last_error(void);
+size_t ckl_noalloc_scratch_bytes(void);
+
 /* Message of the calling thread's most recent non-zero status ("" if none). */
 const char* ckl_last_error(void);
 
