@@ -256,7 +256,7 @@ def run_ours(args) -> None:
     c = c_host.cuda()
     stream = torch.cuda.current_stream()
 
-    algos = {ckl.algo_name(i): i for i in range(6)}
+    algos = {ckl.algo_name(i): i for i in range(ckl.NUM_ALGOS)}
     if args.algo not in algos:
         raise SystemExit(f"--algo must be one of {sorted(algos)}")
     algo = algos[args.algo]

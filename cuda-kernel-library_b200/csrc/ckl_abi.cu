@@ -79,11 +79,11 @@ struct DeviceCtx {
 std::mutex g_ctx_mu;
 std::map<int, std::unique_ptr<DeviceCtx>> g_ctx;
 
-template <bool kPair, typename OutT>
+template <int kMode, typename OutT>
 cudaError_t set_umma_attr() {
-    return cudaFuncSetAttribute(umma_gemm_kernel<kPair, OutT>,
+    return cudaFuncSetAttribute(umma_gemm_kernel<kMode, OutT>,
                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                static_cast<int>(UmmaConfig<kPair>::kSmemBytes));
+                                static_cast<int>(UmmaConfig<kMode>::kSmemBytes));
 }
 
 int get_ctx(DeviceCtx** out) {
@@ -115,18 +115,21 @@ int get_ctx(DeviceCtx** out) {
     ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
     CKL_TRY_CUDA(cudaMalloc(&ctx->status, 4 * sizeof(unsigned int)));
     CKL_TRY_CUDA(cudaMemset(ctx->status, 0, 4 * sizeof(unsigned int)));
-    CKL_TRY_CUDA((set_umma_attr<false, float>()));
-    CKL_TRY_CUDA((set_umma_attr<false, __half>()));
-    CKL_TRY_CUDA((set_umma_attr<false, __nv_bfloat16>()));
-    CKL_TRY_CUDA((set_umma_attr<true, float>()));
-    CKL_TRY_CUDA((set_umma_attr<true, __half>()));
-    CKL_TRY_CUDA((set_umma_attr<true, __nv_bfloat16>()));
+    CKL_TRY_CUDA((set_umma_attr<kModeSingle, float>()));
+    CKL_TRY_CUDA((set_umma_attr<kModeSingle, __half>()));
+    CKL_TRY_CUDA((set_umma_attr<kModeSingle, __nv_bfloat16>()));
+    CKL_TRY_CUDA((set_umma_attr<kModePair, float>()));
+    CKL_TRY_CUDA((set_umma_attr<kModePair, __half>()));
+    CKL_TRY_CUDA((set_umma_attr<kModePair, __nv_bfloat16>()));
+    CKL_TRY_CUDA((set_umma_attr<kModePairWide, float>()));
+    CKL_TRY_CUDA((set_umma_attr<kModePairWide, __half>()));
+    CKL_TRY_CUDA((set_umma_attr<kModePairWide, __nv_bfloat16>()));
     // How many CTA pairs can be resident at once (pairs must share a TPC/GPC).
     {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(static_cast<unsigned>(ctx->sm_count / 2 * 2));
-        cfg.blockDim = dim3(UmmaConfig<true>::kThreads);
-        cfg.dynamicSmemBytes = UmmaConfig<true>::kSmemBytes;
+        cfg.blockDim = dim3(UmmaConfig<kModePairWide>::kThreads);
+        cfg.dynamicSmemBytes = UmmaConfig<kModePairWide>::kSmemBytes;
         cudaLaunchAttribute attr;
         attr.id = cudaLaunchAttributeClusterDimension;
         attr.val.clusterDim.x = 2;
@@ -136,7 +139,7 @@ int get_ctx(DeviceCtx** out) {
         cfg.numAttrs = 1;
         int clusters = 0;
         const cudaError_t e =
-            cudaOccupancyMaxActiveClusters(&clusters, umma_gemm_kernel<true, float>, &cfg);
+            cudaOccupancyMaxActiveClusters(&clusters, umma_gemm_kernel<kModePairWide, float>, &cfg);
         if (e != cudaSuccess || clusters <= 0) {
             (void)cudaGetLastError();
             clusters = ctx->sm_count / 2;
@@ -150,13 +153,46 @@ int get_ctx(DeviceCtx** out) {
 
 size_t dtype_size(int dtype) { return dtype == CKL_F32 ? 4 : 2; }
 
-bool is_tensor_algo(int algo) { return algo >= CKL_ALGO_UMMA_1CTA && algo <= CKL_ALGO_UMMA_2CTA_SK; }
-bool is_pair_algo(int algo) { return algo == CKL_ALGO_UMMA_2CTA || algo == CKL_ALGO_UMMA_2CTA_SK; }
+constexpr int kLastAlgo = CKL_ALGO_UMMA_2CTA_WIDE_SK;
+bool is_tensor_algo(int algo) { return algo >= CKL_ALGO_UMMA_1CTA && algo <= kLastAlgo; }
+int mode_of_algo(int algo) {
+    switch (algo) {
+        case CKL_ALGO_UMMA_2CTA:
+        case CKL_ALGO_UMMA_2CTA_SK: return kModePair;
+        case CKL_ALGO_UMMA_2CTA_WIDE:
+        case CKL_ALGO_UMMA_2CTA_WIDE_SK: return kModePairWide;
+        default: return kModeSingle;
+    }
+}
+bool is_sk_algo(int algo) {
+    return algo == CKL_ALGO_UMMA_SK || algo == CKL_ALGO_UMMA_2CTA_SK ||
+           algo == CKL_ALGO_UMMA_2CTA_WIDE_SK;
+}
+struct ModeDims {
+    int tile_m, tile_n, tile_k;
+    size_t slot_bytes;
+};
+ModeDims dims_of_mode(int mode) {
+    switch (mode) {
+        case kModePair:
+            return {UmmaConfig<kModePair>::kTileM, UmmaConfig<kModePair>::kTileN,
+                    UmmaConfig<kModePair>::kTileK, UmmaConfig<kModePair>::kSlotFloats * sizeof(float)};
+        case kModePairWide:
+            return {UmmaConfig<kModePairWide>::kTileM, UmmaConfig<kModePairWide>::kTileN,
+                    UmmaConfig<kModePairWide>::kTileK,
+                    UmmaConfig<kModePairWide>::kSlotFloats * sizeof(float)};
+        default:
+            return {UmmaConfig<kModeSingle>::kTileM, UmmaConfig<kModeSingle>::kTileN,
+                    UmmaConfig<kModeSingle>::kTileK,
+                    UmmaConfig<kModeSingle>::kSlotFloats * sizeof(float)};
+    }
+}
 
 // ---- planner (pure host arithmetic) ------------------------------------------
 
 struct Plan {
     int algo = CKL_ALGO_SIMT;
+    int mode = kModeSingle;
     bool pair = false;
     int tile_m = 64, tile_n = 64, tile_k = 16;
     int grid = 0;
@@ -169,14 +205,13 @@ bool tma_legal(int k, int lda, int ldb, size_t a_align, size_t b_align) {
 }
 
 // want_sk: 0 = never, 1 = always when a remainder exists, 2 = heuristic.
-Schedule make_schedule(int m, int n, int k, bool pair, int max_units, int want_sk) {
+Schedule make_schedule(int m, int n, int k, int mode, int max_units, int want_sk) {
     Schedule s = {};
-    const int tile_m = pair ? 256 : 128;
-    s.tiles_m = (m + tile_m - 1) / tile_m;
-    s.tiles_n = (n + 255) / 256;
-    const int tile_k = pair ? UmmaConfig<true>::kTileK : UmmaConfig<false>::kTileK;
-    s.k_blocks = (k + tile_k - 1) / tile_k;
-    s.group_m = pair ? 8 : 16;
+    const ModeDims d = dims_of_mode(mode);
+    s.tiles_m = (m + d.tile_m - 1) / d.tile_m;
+    s.tiles_n = (n + d.tile_n - 1) / d.tile_n;
+    s.k_blocks = (k + d.tile_k - 1) / d.tile_k;
+    s.group_m = mode == kModeSingle ? 16 : 8;
     const int tiles = s.tiles_m * s.tiles_n;
     s.units = std::max(1, std::min(max_units, tiles));
     s.dp_tiles = tiles;
@@ -225,14 +260,20 @@ int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_al
         // fill more SMs.
         const long long pair_tiles =
             static_cast<long long>((m + 255) / 256) * static_cast<long long>((n + 255) / 256);
+        const long long wide_tiles =
+            static_cast<long long>((m + 255) / 256) * static_cast<long long>((n + 511) / 512);
+        const bool use_wide = max_pairs > 0 && wide_tiles >= max_pairs;
         const bool use_pair = max_pairs > 0 && pair_tiles >= max_pairs;
-        resolved = !legal ? CKL_ALGO_SIMT : use_pair ? CKL_ALGO_UMMA_2CTA_SK : CKL_ALGO_UMMA_SK;
+        resolved = !legal      ? CKL_ALGO_SIMT
+                   : use_wide ? CKL_ALGO_UMMA_2CTA_WIDE_SK
+                   : use_pair ? CKL_ALGO_UMMA_2CTA_SK
+                              : CKL_ALGO_UMMA_SK;
     } else if (is_tensor_algo(algo) && !legal) {
         return fail(CKL_ERR_UNSUPPORTED,
                     "tensor-core algo %s needs k > 0, A and B 16-byte aligned and lda, ldb "
                     "multiples of 8 elements (lda=%d ldb=%d k=%d)",
                     ckl_algo_name(algo), lda, ldb, k);
-    } else if (algo < CKL_ALGO_AUTO || algo > CKL_ALGO_UMMA_2CTA_SK) {
+    } else if (algo < CKL_ALGO_AUTO || algo > kLastAlgo) {
         return fail(CKL_ERR_INVALID_ARG, "unknown algo %d", algo);
     }
     plan->algo = resolved;
@@ -251,29 +292,32 @@ int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_al
         plan->workspace_bytes = 0;
         return CKL_OK;
     }
-    const bool pair = is_pair_algo(resolved);
+    const int mode = mode_of_algo(resolved);
+    const bool pair = mode != kModeSingle;
     int want_sk = 0;
-    if (resolved == CKL_ALGO_UMMA_SK || resolved == CKL_ALGO_UMMA_2CTA_SK) {
+    if (is_sk_algo(resolved)) {
         want_sk = (algo == CKL_ALGO_AUTO) ? 2 : 1;
     }
     const int max_units = pair ? max_pairs : sm_count;
     if (max_units <= 0) {
         return fail(CKL_ERR_UNSUPPORTED, "no schedulable units (sm_count=%d)", sm_count);
     }
+    const ModeDims d = dims_of_mode(mode);
+    plan->mode = mode;
     plan->pair = pair;
-    plan->tile_m = pair ? 256 : 128;
-    plan->tile_n = 256;
-    plan->tile_k = pair ? UmmaConfig<true>::kTileK : UmmaConfig<false>::kTileK;
-    plan->sched = make_schedule(m, n, k, pair, max_units, want_sk);
+    plan->tile_m = d.tile_m;
+    plan->tile_n = d.tile_n;
+    plan->tile_k = d.tile_k;
+    plan->sched = make_schedule(m, n, k, mode, max_units, want_sk);
     plan->grid = plan->sched.units * (pair ? 2 : 1);
     if (plan->sched.sk_tiles > 0) {
-        const size_t slot = (pair ? UmmaConfig<true>::kSlotFloats : UmmaConfig<false>::kSlotFloats) *
-                            sizeof(float);
-        plan->workspace_bytes = 2ull * static_cast<size_t>(plan->sched.units) * slot;
+        plan->workspace_bytes = 2ull * static_cast<size_t>(plan->sched.units) * d.slot_bytes;
     } else {
         plan->workspace_bytes = 0;
         if (algo == CKL_ALGO_AUTO) {
-            plan->algo = pair ? CKL_ALGO_UMMA_2CTA : CKL_ALGO_UMMA_1CTA;
+            plan->algo = mode == kModePairWide ? CKL_ALGO_UMMA_2CTA_WIDE
+                         : mode == kModePair   ? CKL_ALGO_UMMA_2CTA
+                                               : CKL_ALGO_UMMA_1CTA;
         }
     }
     return CKL_OK;
@@ -324,17 +368,17 @@ int get_workspace(DeviceCtx* ctx, cudaStream_t stream, size_t bytes, float** out
 
 // ---- launches --------------------------------------------------------------------
 
-template <bool kPair, typename OutT>
+template <int kMode, typename OutT>
 int launch_umma(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
                 const GemmParams& p, int grid, cudaStream_t stream) {
-    using Cfg = UmmaConfig<kPair>;
+    using Cfg = UmmaConfig<kMode>;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid));
     cfg.blockDim = dim3(Cfg::kThreads);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr;
-    if (kPair) {
+    if (Cfg::kPair) {
         attr.id = cudaLaunchAttributeClusterDimension;
         attr.val.clusterDim.x = 2;
         attr.val.clusterDim.y = 1;
@@ -342,19 +386,23 @@ int launch_umma(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
     }
-    CKL_TRY_CUDA(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<kPair, OutT>, ta, tb, tc, p));
+    CKL_TRY_CUDA(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<kMode, OutT>, ta, tb, tc, p));
     if (p.sched.sk_tiles > 0) {
-        streamk_fixup_kernel<Cfg::kTileM, OutT><<<p.sched.sk_tiles, 256, 0, stream>>>(p);
+        streamk_fixup_kernel<Cfg::kTileM, Cfg::kTileN, OutT>
+            <<<p.sched.sk_tiles, 256, 0, stream>>>(p);
         CKL_TRY_CUDA(cudaGetLastError());
     }
     return CKL_OK;
 }
 
 template <typename OutT>
-int launch_umma_out(bool pair, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+int launch_umma_out(int mode, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
                     const GemmParams& p, int grid, cudaStream_t stream) {
-    return pair ? launch_umma<true, OutT>(ta, tb, tc, p, grid, stream)
-                : launch_umma<false, OutT>(ta, tb, tc, p, grid, stream);
+    switch (mode) {
+        case kModePair: return launch_umma<kModePair, OutT>(ta, tb, tc, p, grid, stream);
+        case kModePairWide: return launch_umma<kModePairWide, OutT>(ta, tb, tc, p, grid, stream);
+        default: return launch_umma<kModeSingle, OutT>(ta, tb, tc, p, grid, stream);
+    }
 }
 
 template <typename InT, typename OutT>
@@ -406,7 +454,7 @@ int gemm_impl(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, 
         return fail(CKL_ERR_INVALID_ARG, "C dtype must be CKL_F32, CKL_F16 or CKL_BF16 (got %d)",
                     c_dtype);
     }
-    if (algo < CKL_ALGO_AUTO || algo > CKL_ALGO_UMMA_2CTA_SK) {
+    if (algo < CKL_ALGO_AUTO || algo > kLastAlgo) {
         return fail(CKL_ERR_INVALID_ARG, "unknown algo %d", algo);
     }
     if (m <= 0 || n <= 0) {
@@ -517,9 +565,9 @@ int gemm_impl(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, 
         }
     }
     switch (c_dtype) {
-        case CKL_F32: return launch_umma_out<float>(plan.pair, ta, tb, tc, p, plan.grid, stream);
-        case CKL_F16: return launch_umma_out<__half>(plan.pair, ta, tb, tc, p, plan.grid, stream);
-        default: return launch_umma_out<__nv_bfloat16>(plan.pair, ta, tb, tc, p, plan.grid, stream);
+        case CKL_F32: return launch_umma_out<float>(plan.mode, ta, tb, tc, p, plan.grid, stream);
+        case CKL_F16: return launch_umma_out<__half>(plan.mode, ta, tb, tc, p, plan.grid, stream);
+        default: return launch_umma_out<__nv_bfloat16>(plan.mode, ta, tb, tc, p, plan.grid, stream);
     }
 }
 
@@ -825,6 +873,8 @@ const char* ckl_algo_name(int algo) {
         case CKL_ALGO_UMMA_SK: return "umma_1cta_streamk";
         case CKL_ALGO_UMMA_2CTA: return "umma_2cta";
         case CKL_ALGO_UMMA_2CTA_SK: return "umma_2cta_streamk";
+        case CKL_ALGO_UMMA_2CTA_WIDE: return "umma_2cta_wide";
+        case CKL_ALGO_UMMA_2CTA_WIDE_SK: return "umma_2cta_wide_streamk";
         default: return "unknown";
     }
 }

@@ -78,6 +78,9 @@ struct GemmParams {
 #ifndef CKL_STAGES_2CTA
 #define CKL_STAGES_2CTA 3
 #endif
+#ifndef CKL_STAGES_WIDE
+#define CKL_STAGES_WIDE 3
+#endif
 
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
@@ -87,14 +90,27 @@ enum StatusCode : unsigned int {
 };
 enum Role : unsigned int { kRoleProducer = 1, kRoleMma = 2, kRoleEpilogue = 3, kRoleDrain = 4 };
 
-template <bool kPair>
+// Kernel shapes.  kModeSingle: one CTA per 128x256 tile.  kModePair: a CTA pair per
+// 256x256 tile, two accumulators in TMEM (epilogue fully overlapped).  kModePairWide: a CTA
+// pair per 256x512 tile; the accumulator fills all 512 TMEM columns, so each loaded row of
+// A feeds twice as many columns (a quarter less L2-to-SM traffic, the dominant data-movement
+// cost under the power cap) at the price of draining TMEM between tiles, which eight
+// epilogue warps keep short.
+enum KernelMode : int { kModeSingle = 0, kModePair = 1, kModePairWide = 2 };
+
+template <int kMode>
 struct UmmaConfig {
-    static constexpr int kStages = kPair ? CKL_STAGES_2CTA : CKL_STAGES_1CTA;
-    static constexpr int kBBoxes = kPair ? 2 : 4;  // 64-column boxes of B per CTA per 64 k rows
-    // A stage holds kKSub sub-blocks of 64 k elements.  The CTA pair takes 128 k per stage:
-    // every tcgen05.commit that frees a stage costs the pair a cross-SM round trip, and
-    // eight MMAs per commit instead of four amortise it.
-    static constexpr int kKSub = kPair ? 2 : 1;
+    static constexpr bool kPair = kMode != kModeSingle;
+    static constexpr bool kWide = kMode == kModePairWide;
+    static constexpr int kStages =
+        kWide ? CKL_STAGES_WIDE : (kPair ? CKL_STAGES_2CTA : CKL_STAGES_1CTA);
+    static constexpr int kNHalves = kWide ? 2 : 1;  // 256-column accumulator halves per tile
+    // 64-column boxes of B this CTA loads per 64 k rows
+    static constexpr int kBBoxes = kMode == kModePair ? 2 : 4;
+    // A stage holds kKSub sub-blocks of 64 k elements.  Freeing a stage costs the pair a
+    // cross-SM tcgen05.commit round trip, so a pair stage always carries eight MMAs:
+    // 128 k of one 256-column accumulator, or 64 k of two.
+    static constexpr int kKSub = kMode == kModePair ? 2 : 1;
     static constexpr uint32_t kASubBytes = 128 * 64 * 2;
     static constexpr uint32_t kBoxBytes = 64 * 64 * 2;
     static constexpr uint32_t kBSubBytes = kBBoxes * kBoxBytes;
@@ -103,15 +119,17 @@ struct UmmaConfig {
     static constexpr uint32_t kStageBytes = kABytes + kBBytes;
     static constexpr uint32_t kTxBytes = kStageBytes * (kPair ? 2 : 1);
     static constexpr int kTileM = kPair ? 256 : 128;
-    static constexpr int kTileN = 256;
+    static constexpr int kTileN = 256 * kNHalves;
     static constexpr int kTileK = 64 * kKSub;
+    static constexpr int kAccStages = kWide ? 1 : 2;
+    static constexpr int kEpiWarps = kWide ? 8 : 4;
+    static constexpr int kThreads = 64 + 32 * kEpiWarps;
     // Epilogue staging: per epilogue warp two buffers of 32 rows x 128 B.
-    static constexpr uint32_t kStagingBytes = 4 * 2 * 4096;
-    static constexpr int kNumBarriers = 2 * kStages + 5 + 8;
+    static constexpr uint32_t kStagingBytes = kEpiWarps * 2 * 4096;
+    static constexpr int kNumBarriers = 2 * kStages + 5 + 2 * kEpiWarps;
     // ring + staging + barriers + TMEM slot + abort flag, plus slack to 1024-align the ring
     static constexpr uint32_t kSmemBytes =
         kStages * kStageBytes + kStagingBytes + kNumBarriers * 8 + 16 + 1024;
-    static constexpr int kThreads = 192;
     static constexpr size_t kSlotFloats = static_cast<size_t>(kTileM) * kTileN;
 };
 
@@ -150,10 +168,10 @@ __device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, cons
     unsigned long long t0 = 0;
     unsigned int spins = 0;
     while (true) {
-        if (ptx::mbar_try_wait(bar, parity)) {
+        if (ptx::mbar_try_wait_parked(bar, parity, 4000u)) {
             return true;
         }
-        if ((++spins & 127u) == 0u) {
+        if ((++spins & 15u) == 0u) {
             if (*ctl.abort_flag != 0) {
                 return false;
             }
@@ -312,12 +330,14 @@ __device__ __forceinline__ void finish_row_chunk(float (&acc)[32], OutT* row_ptr
 
 }  // namespace detail
 
-template <bool kPair, typename OutT>
-__global__ void __launch_bounds__(192, 1)
+template <int kMode, typename OutT>
+__global__ void __launch_bounds__(UmmaConfig<kMode>::kThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
-    using Cfg = UmmaConfig<kPair>;
+    using Cfg = UmmaConfig<kMode>;
+    constexpr bool kPair = Cfg::kPair;
+    constexpr bool kWide = Cfg::kWide;
     constexpr int kStages = Cfg::kStages;
 #ifdef CKL_EXPERIMENT
     const unsigned long long prof_entry = ptx::global_timer_ns();
@@ -371,7 +391,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ptx::mbar_init(acc_empty_bar(a), kPair ? 8 : 4);
         }
         ptx::mbar_init(drain_bar, 1);
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < Cfg::kEpiWarps; ++w) {
             ptx::mbar_init(cin_bar(w, 0), 1);
             ptx::mbar_init(cin_bar(w, 1), 1);
         }
@@ -420,6 +440,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // TMA producer.
             SegmentCursor cur = make_cursor(sched, unit);
             Segment seg;
+#ifdef CKL_EXPERIMENT
+            const uint64_t hints[3] = {ptx::kL2EvictNormal, ptx::kL2EvictFirst, ptx::kL2EvictLast};
+            const uint64_t hint_a = hints[(p.debug >> 8) & 3], hint_b = hints[(p.debug >> 10) & 3];
+#else
+            constexpr uint64_t hint_a = ptx::kL2EvictNormal, hint_b = ptx::kL2EvictNormal;
+#endif
             uint32_t it = 0;       // k blocks issued so far
             int stage = 0;         // it % kStages
             uint32_t phase = 0;    // (it / kStages) & 1
@@ -463,18 +489,22 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             const uint32_t a_sub = a_dst + sub * Cfg::kASubBytes;
                             const uint32_t b_sub = b_dst + sub * Cfg::kBSubBytes;
                             if constexpr (kPair) {
-                                ptx::tma_load_2d_pair(a_sub, &tmap_a, bar, k0, a_row);
+                                ptx::tma_load_2d_pair_hint(a_sub, &tmap_a, bar, k0, a_row, hint_a);
                             } else {
-                                ptx::tma_load_2d(a_sub, &tmap_a, bar, k0, a_row);
+                                ptx::tma_load_2d_hint(a_sub, &tmap_a, bar, k0, a_row, hint_a);
                             }
 #pragma unroll
                             for (int j = 0; j < Cfg::kBBoxes; ++j) {
+                                // wide tile: boxes 0,1 belong to columns 0-255 of the tile,
+                                // boxes 2,3 to columns 256-511 (this CTA's 128 of each)
+                                const int box_col =
+                                    kWide ? b_col + (j >> 1) * 256 + (j & 1) * 64 : b_col + j * 64;
                                 if constexpr (kPair) {
-                                    ptx::tma_load_2d_pair(b_sub + j * Cfg::kBoxBytes, &tmap_b, bar,
-                                                          b_col + j * 64, k0);
+                                    ptx::tma_load_2d_pair_hint(b_sub + j * Cfg::kBoxBytes, &tmap_b, bar,
+                                                               box_col, k0, hint_b);
                                 } else {
-                                    ptx::tma_load_2d(b_sub + j * Cfg::kBoxBytes, &tmap_b, bar,
-                                                     b_col + j * 64, k0);
+                                    ptx::tma_load_2d_hint(b_sub + j * Cfg::kBoxBytes, &tmap_b, bar,
+                                                          box_col, k0, hint_b);
                                 }
                             }
                         }
@@ -518,12 +548,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t seg_count = 0;
             bool ok = true;
             while (ok && next_segment(sched, &cur, &seg)) {
-                const uint32_t acc = seg_count & 1u;
-                const uint32_t acc_use = seg_count >> 1;
+                // Two accumulators, used alternately (kAccStages == 2), or one accumulator
+                // of two 256-column halves that the epilogue hands back one by one.
+                const uint32_t acc = kWide ? 0u : (seg_count & 1u);
+                const uint32_t acc_parity = kWide ? (seg_count & 1u) : ((seg_count >> 1) & 1u);
                 {
                     CKL_PROF_BEGIN();
-                    const bool got = detail::wait_barrier(acc_empty_bar(acc), (acc_use & 1u) ^ 1u,
-                                                          ctl, kRoleMma, 0x80000000u | seg_count);
+                    bool got = detail::wait_barrier(acc_empty_bar(static_cast<int>(acc)),
+                                                    acc_parity ^ 1u, ctl, kRoleMma,
+                                                    0x80000000u | seg_count);
+                    if (kWide && got) {
+                        got = detail::wait_barrier(acc_empty_bar(1), acc_parity ^ 1u, ctl, kRoleMma,
+                                                   0x90000000u | seg_count);
+                    }
                     CKL_PROF_END(prof_wait2);
                     if (!got) {
                         ok = false;
@@ -576,15 +613,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         // fourth instruction moves on to the next 64-k sub-block of the stage.
                         const uint64_t a_off = static_cast<uint64_t>(
                             ((j >> 2) * Cfg::kASubBytes + (j & 3) * 32) >> 4);
-                        const uint64_t b_off = static_cast<uint64_t>(
-                            ((j >> 2) * Cfg::kBSubBytes + (j & 3) * 2048) >> 4);
                         const uint32_t accumulate = (kb > seg.kb_begin || j > 0) ? 1u : 0u;
-                        if constexpr (kPair) {
-                            ptx::umma_f16_pair(d_tmem, a_desc + a_off, b_desc + b_off, p.idesc,
-                                               accumulate);
-                        } else {
-                            ptx::umma_f16(d_tmem, a_desc + a_off, b_desc + b_off, p.idesc,
-                                          accumulate);
+#pragma unroll
+                        for (int h = 0; h < Cfg::kNHalves; ++h) {
+                            // wide tile: the same A rows against the two 256-column halves of B
+                            const uint64_t b_off = static_cast<uint64_t>(
+                                ((j >> 2) * Cfg::kBSubBytes + h * 2 * Cfg::kBoxBytes + (j & 3) * 2048) >> 4);
+                            if constexpr (kPair) {
+                                ptx::umma_f16_pair(d_tmem + h * 256u, a_desc + a_off, b_desc + b_off,
+                                                   p.idesc, accumulate);
+                            } else {
+                                ptx::umma_f16(d_tmem + h * 256u, a_desc + a_off, b_desc + b_off,
+                                              p.idesc, accumulate);
+                            }
                         }
                         if (j == 0 && kb + 1 < seg.kb_end) {
                             ready = ptx::mbar_try_wait(full_bar(next_stage), next_phase);
@@ -638,10 +679,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if (ok) {
                 // Tail: the epilogue (of both CTAs) must have drained the last
                 // accumulators before TMEM can go.
-                const uint32_t first = seg_count > 2u ? seg_count - 2u : 0u;
-                for (uint32_t i = first; i < seg_count && ok; ++i) {
-                    ok = detail::wait_barrier(acc_empty_bar(i & 1u), (i >> 1) & 1u, ctl, kRoleDrain,
-                                              0x80000000u | i);
+                if constexpr (kWide) {
+                    if (seg_count > 0) {
+                        const uint32_t i = seg_count - 1u;
+                        ok = detail::wait_barrier(acc_empty_bar(0), i & 1u, ctl, kRoleDrain,
+                                                  0x80000000u | i) &&
+                             detail::wait_barrier(acc_empty_bar(1), i & 1u, ctl, kRoleDrain,
+                                                  0x90000000u | i);
+                    }
+                } else {
+                    const uint32_t first = seg_count > 2u ? seg_count - 2u : 0u;
+                    for (uint32_t i = first; i < seg_count && ok; ++i) {
+                        ok = detail::wait_barrier(acc_empty_bar(i & 1u), (i >> 1) & 1u, ctl,
+                                                  kRoleDrain, 0x80000000u | i);
+                    }
                 }
             } else {
                 // Aborting: wait (bounded) until the MMAs already issued have retired.
@@ -654,9 +705,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
         }
     } else {
-        // Epilogue warps 2..5; TMEM lane quarter = warp id mod 4.
+        // Epilogue warps 2..; TMEM lane quarter = warp id mod 4.  With the wide tile, warps
+        // 2-5 drain columns 0-255 of the accumulator and warps 6-9 columns 256-511.
         const uint32_t quad = static_cast<uint32_t>(warp) & 3u;
         const int ew = warp - 2;  // staging slice of this warp
+        const uint32_t half = kWide ? static_cast<uint32_t>(ew >> 2) : 0u;
         SegmentCursor cur = make_cursor(sched, unit);
         Segment seg;
         uint32_t seg_count = 0;
@@ -665,7 +718,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // TMA epilogue state: two 4 KB staging buffers (32 rows x 128 B, 128-byte
         // swizzle), one C_in barrier each; bit b of cin_parity = next phase to wait for.
         constexpr int kChunkCols = 128 / static_cast<int>(sizeof(OutT));
-        constexpr int kChunks = Cfg::kTileN / kChunkCols;
+        constexpr int kChunks = 256 / kChunkCols;  // a warp always drains 256 columns
         constexpr int kUnitElems = 16 / static_cast<int>(sizeof(OutT));
         const uint32_t stg = staging + static_cast<uint32_t>(ew) * 8192u;
         uint8_t* stg_ptr = staging_ptr + ew * 8192;
@@ -674,16 +727,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const bool reads_c = (p.epi_mode == kEpiLinear) && (p.beta != 0.0f);
         bool alive = true;
         while (alive && next_segment(sched, &cur, &seg)) {
-            const uint32_t acc = seg_count & 1u;
-            const uint32_t acc_use = seg_count >> 1;
+            const uint32_t acc = kWide ? 0u : (seg_count & 1u);
+            const uint32_t acc_parity = kWide ? (seg_count & 1u) : ((seg_count >> 1) & 1u);
+            const uint32_t acc_cols = kWide ? half * 256u : acc * 256u;  // TMEM column offset
             int tm, tn;
             tile_coords(sched, seg.tile, &tm, &tn);
             const int row_in_tile = (kPair ? static_cast<int>(rank) * 128 : 0) +
                                     static_cast<int>(quad) * 32 + static_cast<int>(lane);
             const int row = tm * Cfg::kTileM + row_in_tile;
             const int row0 = row - static_cast<int>(lane);  // first row of this warp
-            const int col_base = tn * Cfg::kTileN;
-            const uint32_t t_row = tmem_base + ((quad * 32u) << 16) + acc * 256u;
+            const int col_base = tn * Cfg::kTileN + static_cast<int>(half) * 256;
+            const uint32_t t_row = tmem_base + ((quad * 32u) << 16) + acc_cols;
             const bool tma_path = (p.c_tma != 0) && seg.slot < 0;
             const bool warp_has_rows = row0 < p.m;
 
@@ -696,8 +750,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
             int ok = 1;
             if (lane == 0) {
-                ok = detail::wait_barrier(acc_full_bar(acc), acc_use & 1u, ctl, kRoleEpilogue,
-                                          seg_count)
+                ok = detail::wait_barrier(acc_full_bar(static_cast<int>(acc)), acc_parity, ctl,
+                                          kRoleEpilogue, seg_count)
                          ? 1
                          : 0;
             }
@@ -707,7 +761,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
             // Every lane observes the completed phase itself (acquire); it cannot
             // advance again before this warp releases the accumulator below.
-            for (int i = 0; i < 1024 && !ptx::mbar_try_wait(acc_full_bar(acc), acc_use & 1u); ++i) {
+            for (int i = 0;
+                 i < 1024 && !ptx::mbar_try_wait(acc_full_bar(static_cast<int>(acc)), acc_parity); ++i) {
             }
             ptx::tc_fence_after_sync();
 
@@ -718,9 +773,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if (seg.slot >= 0) {
                 // Partial accumulator -> FP32 workspace slot, full tile, no predication.
                 float* dst = p.workspace + static_cast<size_t>(seg.slot) * Cfg::kSlotFloats +
-                             static_cast<size_t>(row_in_tile) * Cfg::kTileN;
+                             static_cast<size_t>(row_in_tile) * Cfg::kTileN + half * 256u;
 #pragma unroll 1
-                for (int c = 0; c < Cfg::kTileN / 32; ++c) {
+                for (int c = 0; c < 256 / 32; ++c) {
                     uint32_t r[32];
                     ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), r);
                     ptx::tmem_ld_wait();
@@ -830,7 +885,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 OutT* row_ptr = c_base + static_cast<size_t>(row) * static_cast<size_t>(p.ldc);
                 const bool row_ok = row < p.m;
 #pragma unroll 1
-                for (int c = 0; c < Cfg::kTileN / 32; ++c) {
+                for (int c = 0; c < 256 / 32; ++c) {
                     if (col_base + c * 32 >= p.n) {
                         break;  // uniform across the warp
                     }
@@ -852,10 +907,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) {
+                const int release = static_cast<int>(kWide ? half : acc);
                 if constexpr (kPair) {
-                    ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_empty_bar(acc), 0));
+                    ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_empty_bar(release), 0));
                 } else {
-                    ptx::mbar_arrive(acc_empty_bar(acc));
+                    ptx::mbar_arrive(acc_empty_bar(release));
                 }
                 if (tma_path) {
                     ptx::bulk_wait_group_read<0>();  // staging is reusable by the next tile
@@ -905,10 +961,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // partials of the tile in ascending unit order and applies the epilogue.
 // Tiles that a single unit covered whole were already written by the GEMM
 // kernel and are skipped.
-template <int kTileM, typename OutT>
+template <int kTileM, int kTileN, typename OutT>
 __global__ void __launch_bounds__(256)
 streamk_fixup_kernel(const GemmParams p) {
-    constexpr int kTileN = 256;
     constexpr size_t kSlotFloats = static_cast<size_t>(kTileM) * kTileN;
     const Schedule& s = p.sched;
     const int sk_tile = static_cast<int>(blockIdx.x);

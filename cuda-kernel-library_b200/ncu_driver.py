@@ -41,7 +41,7 @@ def main() -> None:
     sys.modules["ckl_b200"] = ckl
     spec.loader.exec_module(ckl)
 
-    algos = {ckl.algo_name(i): i for i in range(6)}
+    algos = {ckl.algo_name(i): i for i in range(ckl.NUM_ALGOS)}
     if args.algo not in algos:
         raise SystemExit(f"--algo must be one of {sorted(algos)}")
     tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}

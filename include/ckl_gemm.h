@@ -51,7 +51,9 @@ typedef enum ckl_algo {
     CKL_ALGO_UMMA_1CTA = 2,  /* TMA + tcgen05.mma, one CTA per 128x256 tile, data-parallel */
     CKL_ALGO_UMMA_SK = 3,    /* same kernel with the stream-K split of the tile remainder */
     CKL_ALGO_UMMA_2CTA = 4,  /* CTA-pair tcgen05.mma (cta_group::2), 256x256 tile per pair */
-    CKL_ALGO_UMMA_2CTA_SK = 5
+    CKL_ALGO_UMMA_2CTA_SK = 5,
+    CKL_ALGO_UMMA_2CTA_WIDE = 6, /* CTA pair, 256x512 tile filling all of tensor memory */
+    CKL_ALGO_UMMA_2CTA_WIDE_SK = 7
 } ckl_algo;
 
 /* Stream handle: a cudaStream_t passed as an opaque pointer so this header

@@ -83,7 +83,10 @@ def test_dispatch_follows_the_reference_contract(ckl):
     assert e.value.status == ckl.ERR_UNSUPPORTED
     # large problems: CTA pairs, 256x256 tile, 128 k per stage
     p = ckl.plan_gemm(8192, 8192, 8192)
-    assert p.algo == ckl.ALGO_UMMA_2CTA
+    assert p.algo == ckl.ALGO_UMMA_2CTA_WIDE
+    assert (p.tile_m, p.tile_n, p.tile_k) == (256, 512, 64)
+    assert (p.tiles_m, p.tiles_n, p.k_blocks, p.grid, p.units) == (32, 16, 128, 148, 74)
+    p = ckl.plan_gemm(8192, 8192, 8192, algo=ckl.ALGO_UMMA_2CTA)
     assert (p.tile_m, p.tile_n, p.tile_k) == (256, 256, 128)
     assert (p.tiles_m, p.tiles_n, p.k_blocks, p.grid, p.units) == (32, 32, 64, 148, 74)
     p = ckl.plan_gemm(8192, 8192, 8192, algo=ckl.ALGO_UMMA_1CTA)
@@ -92,7 +95,7 @@ def test_dispatch_follows_the_reference_contract(ckl):
     # the skinny stream-K stress shape splits by default; forcing the split works anywhere
     p = ckl.plan_gemm(1024, 1024, 32768)
     assert p.algo == ckl.ALGO_UMMA_SK and p.sk_tiles == 32 and p.workspace_bytes > 0
-    for algo in (ckl.ALGO_UMMA_SK, ckl.ALGO_UMMA_2CTA_SK):
+    for algo in (ckl.ALGO_UMMA_SK, ckl.ALGO_UMMA_2CTA_SK, ckl.ALGO_UMMA_2CTA_WIDE_SK):
         p = ckl.plan_gemm(4000, 3000, 5000, algo=algo)
         assert p.sk_tiles > 0 and p.workspace_bytes > 0
 
@@ -100,7 +103,8 @@ def test_dispatch_follows_the_reference_contract(ckl):
 SHAPES = [(128, 256, 64), (256, 256, 256), (4000, 3000, 5000), (1024, 1024, 32768),
           (8192, 8192, 8192), (8192, 1024, 8192), (16384, 1792, 4096), (200, 264, 72),
           (2304, 4096, 1024), (1000, 776, 520), (128, 256, 6400), (100000, 256, 64)]
-ALGOS = ["ALGO_UMMA_1CTA", "ALGO_UMMA_SK", "ALGO_UMMA_2CTA", "ALGO_UMMA_2CTA_SK"]
+ALGOS = ["ALGO_UMMA_1CTA", "ALGO_UMMA_SK", "ALGO_UMMA_2CTA", "ALGO_UMMA_2CTA_SK",
+         "ALGO_UMMA_2CTA_WIDE", "ALGO_UMMA_2CTA_WIDE_SK"]
 
 
 @pytest.mark.parametrize("sm_count", [148, 132, 8])
@@ -114,6 +118,7 @@ def test_schedule_covers_every_k_block_once(ckl, shape, algo_name, sm_count):
     assert plan.k_blocks == -(-k // plan.tile_k)
     assert plan.dp_tiles + plan.sk_tiles == tiles
     pair = plan.tile_m == 256
+    assert plan.tile_n == (512 if "WIDE" in algo_name else 256)
     assert plan.grid == plan.units * (2 if pair else 1)
     assert plan.units <= (sm_count // 2 if pair else sm_count)
 

@@ -155,7 +155,7 @@ def test_beta_zero_does_not_read_c(env):
     m, n, k = 256, 512, 128
     da, ra = env.narrow_dev(orc.random_matrix(m, k, 1), ckl.F16)
     db, rb = env.narrow_dev(orc.random_matrix(k, n, 2), ckl.F16)
-    for algo in (ckl.ALGO_SIMT, ckl.ALGO_UMMA_1CTA, ckl.ALGO_UMMA_2CTA):
+    for algo in (ckl.ALGO_SIMT, ckl.ALGO_UMMA_1CTA, ckl.ALGO_UMMA_2CTA, ckl.ALGO_UMMA_2CTA_WIDE):
         c = torch.full((m, n), float("nan"), device="cuda")
         ckl.gemm_ex(ckl.F16, da, db, c, ckl.F32, m, n, k, k, n, n, 1.0, 0.0, algo)
         assert not torch.isnan(c).any()
@@ -165,7 +165,8 @@ def test_beta_zero_does_not_read_c(env):
 # every kernel, every output type, alpha / beta, ragged shapes
 # ---------------------------------------------------------------------------------------
 
-ALGO_NAMES = ["ALGO_SIMT", "ALGO_UMMA_1CTA", "ALGO_UMMA_SK", "ALGO_UMMA_2CTA", "ALGO_UMMA_2CTA_SK"]
+ALGO_NAMES = ["ALGO_SIMT", "ALGO_UMMA_1CTA", "ALGO_UMMA_SK", "ALGO_UMMA_2CTA", "ALGO_UMMA_2CTA_SK",
+              "ALGO_UMMA_2CTA_WIDE", "ALGO_UMMA_2CTA_WIDE_SK"]
 RAGGED = [(128, 256, 64), (200, 264, 72), (1000, 776, 520), (130, 8, 8), (1, 2048, 4096),
           (513, 1032, 1000), (2304, 1280, 2048)]
 
@@ -200,7 +201,7 @@ def test_results_are_deterministic(env):
     m, n, k = 4000, 3000, 1000
     da, _ = env.narrow_dev(orc.random_matrix(m, k, 3), ckl.F16)
     db, _ = env.narrow_dev(orc.random_matrix(k, n, 4), ckl.F16)
-    for algo in (ckl.ALGO_AUTO, ckl.ALGO_UMMA_SK, ckl.ALGO_UMMA_2CTA_SK):
+    for algo in (ckl.ALGO_AUTO, ckl.ALGO_UMMA_SK, ckl.ALGO_UMMA_2CTA_SK, ckl.ALGO_UMMA_2CTA_WIDE_SK):
         outs = []
         for _ in range(3):
             c = torch.zeros(m, n, device="cuda")
@@ -337,12 +338,18 @@ def test_config_bf16_8192_cubed_beta(env):
     _run_large(env, 8192, 8192, 8192, env.ckl.BF16, env.ckl.BF16, 1.0, 0.5, "normal002", 8, 8)
 
 
+def test_config_bf16_8192_cubed_pair_kernel(env):
+    _run_large(env, 8192, 8192, 8192, env.ckl.BF16, env.ckl.BF16, 1.0, 0.5, "normal002", 6, 6,
+               algo=env.ckl.ALGO_UMMA_2CTA)
+
+
 def test_config_bf16_8192_cubed_single_cta_kernel(env):
     _run_large(env, 8192, 8192, 8192, env.ckl.BF16, env.ckl.F32, 1.0, 0.0, "normal002", 6, 6,
                algo=env.ckl.ALGO_UMMA_SK)
 
 
-@pytest.mark.parametrize("algo_name", ["ALGO_AUTO", "ALGO_UMMA_SK", "ALGO_UMMA_2CTA_SK"])
+@pytest.mark.parametrize("algo_name", ["ALGO_AUTO", "ALGO_UMMA_SK", "ALGO_UMMA_2CTA_SK",
+                                       "ALGO_UMMA_2CTA_WIDE_SK"])
 def test_config_streamk_ragged(env, algo_name):
     algo = getattr(env.ckl, algo_name)
     if algo != env.ckl.ALGO_AUTO:
