@@ -262,7 +262,11 @@ int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_al
             static_cast<long long>((m + 255) / 256) * static_cast<long long>((n + 255) / 256);
         const long long wide_tiles =
             static_cast<long long>((m + 255) / 256) * static_cast<long long>((n + 511) / 512);
-        const bool use_wide = max_pairs > 0 && wide_tiles >= max_pairs;
+        // The wide tile saves a quarter of the L2-to-SM traffic (higher clocks under the power
+        // cap) but exposes its epilogue between tiles; measured, it wins only when the
+        // main loop is long (k >= 8192) and no tile column is mostly padding.
+        const bool use_wide = max_pairs > 0 && wide_tiles >= max_pairs && k >= 8192 &&
+                              (n % 512 == 0 || n % 512 > 384);
         const bool use_pair = max_pairs > 0 && pair_tiles >= max_pairs;
         resolved = !legal      ? CKL_ALGO_SIMT
                    : use_wide ? CKL_ALGO_UMMA_2CTA_WIDE_SK

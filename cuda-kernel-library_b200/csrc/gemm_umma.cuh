@@ -213,6 +213,10 @@ struct OutTraits<float> {
     static __device__ __forceinline__ void store_vec(float* p, const float* v) {
         *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
     }
+    static __device__ __forceinline__ void unpack(const uint4& t, float (&v)[4]) {
+        v[0] = __uint_as_float(t.x); v[1] = __uint_as_float(t.y);
+        v[2] = __uint_as_float(t.z); v[3] = __uint_as_float(t.w);
+    }
 };
 template <>
 struct OutTraits<__half> {
@@ -221,6 +225,15 @@ struct OutTraits<__half> {
     static __device__ __forceinline__ void store(__half* p, float v) { *p = __float2half_rn(v); }
     static __device__ __forceinline__ void load_vec(const __half* p, float (&v)[8]) {
         const uint4 t = *reinterpret_cast<const uint4*>(p);
+        const __half2* h = reinterpret_cast<const __half2*>(&t);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h[i]);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void unpack(const uint4& t, float (&v)[8]) {
         const __half2* h = reinterpret_cast<const __half2*>(&t);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -250,6 +263,15 @@ struct OutTraits<__nv_bfloat16> {
     }
     static __device__ __forceinline__ void load_vec(const __nv_bfloat16* p, float (&v)[8]) {
         const uint4 t = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&t);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h[i]);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void unpack(const uint4& t, float (&v)[8]) {
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&t);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -509,6 +531,30 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             }
                         }
                     }
+                    if constexpr (kWide) {
+                        // Wide tile: the epilogue sits between two tiles, so its C_in must
+                        // not come from DRAM.  While the last k blocks of the tile stream
+                        // in, pull this CTA's 128 x 512 block of C into L2, four boxes
+                        // (32 rows x 128 B each) per k block.
+                        constexpr int kBoxCols = 128 / static_cast<int>(sizeof(OutT));
+                        constexpr int kBoxesPerRowGroup = Cfg::kTileN / kBoxCols;
+                        constexpr int kBoxes = 4 * kBoxesPerRowGroup;
+                        constexpr int kLead = kBoxes / 4 + 4;  // k blocks before the end
+                        const int left = seg.kb_end - kb;
+                        if (p.c_tma && p.beta != 0.0f && p.epi_mode == kEpiLinear && seg.slot < 0 &&
+                            left <= kLead && left > 4) {
+                            const int first = (kLead - left) * 4;
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const int box = first + q;
+                                const int r0 = a_row + (box / kBoxesPerRowGroup) * 32;
+                                const int c0 = tn * Cfg::kTileN + (box % kBoxesPerRowGroup) * kBoxCols;
+                                if (r0 < p.m && c0 < p.n) {
+                                    ptx::tma_prefetch_l2_2d(&tmap_c, c0, r0);
+                                }
+                            }
+                        }
+                    }
                     ++it;
                     if (++stage == kStages) {
                         stage = 0;
@@ -670,8 +716,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #ifdef CKL_EXPERIMENT
             if (p.prof) {
                 p.prof[blockIdx.x * 8 + 0] = static_cast<unsigned long long>(clock64() - prof_c0);
-                p.prof[blockIdx.x * 8 + 1] = ptx::global_timer_ns();   // MMA loop done (absolute)
-                p.prof[blockIdx.x * 8 + 4] = static_cast<unsigned long long>(prof_wait);
                 p.prof[blockIdx.x * 8 + 5] = static_cast<unsigned long long>(prof_wait2);
                 p.prof[blockIdx.x * 8 + 6] = it;
             }
@@ -725,6 +769,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t cin_parity = 0;
         uint32_t cin_pending = 0;  // lane 0: loads issued and not yet waited for
         const bool reads_c = (p.epi_mode == kEpiLinear) && (p.beta != 0.0f);
+#ifdef CKL_EXPERIMENT
+        long long ep[5] = {0, 0, 0, 0, 0};
+#endif
         bool alive = true;
         while (alive && next_segment(sched, &cur, &seg)) {
             const uint32_t acc = kWide ? 0u : (seg_count & 1u);
@@ -797,22 +844,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         }
                         const uint32_t b = static_cast<uint32_t>(c) & 1u;
                         const bool next_chunk = (c + 1 < kChunks) && (col + kChunkCols < p.n);
-                        if (reads_c) {
-                            if (next_chunk && lane == 0) {
-                                // buffer b^1 was the source of the previous chunk's store
-                                ptx::bulk_wait_group_read<0>();
-                                ptx::mbar_arrive_expect_tx(cin_bar(ew, b ^ 1u), 4096);
-                                ptx::tma_load_2d(stg + (b ^ 1u) * 4096u, &tmap_c, cin_bar(ew, b ^ 1u),
-                                                 col + kChunkCols, row0);
-                                cin_pending |= 1u << (b ^ 1u);
-                            }
-                        } else {
+#ifdef CKL_EXPERIMENT
+                        long long ep_t = clock64();
+#endif
+                        if (!reads_c) {
                             // buffer b was the source of the store two chunks ago
                             if (lane == 0) {
                                 ptx::bulk_wait_group_read<1>();
                             }
                             __syncwarp();
                         }
+#ifdef CKL_EXPERIMENT
+                        { const long long n_ = clock64(); ep[0] += n_ - ep_t; ep_t = n_; }
+#endif
                         float acc_f[kChunkCols];
 #pragma unroll
                         for (int h = 0; h < kChunkCols / 32; ++h) {
@@ -825,6 +869,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                 acc_f[h * 32 + e] = __uint_as_float(r[e]);
                             }
                         }
+#ifdef CKL_EXPERIMENT
+                        { const long long n_ = clock64(); ep[1] += n_ - ep_t; ep_t = n_; }
+#endif
                         if (reads_c) {
                             int got = 1;
                             if (lane == 0) {
@@ -845,7 +892,31 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             }
                             cin_parity ^= 1u << b;
                         }
+#ifdef CKL_EXPERIMENT
+                        { const long long n_ = clock64(); ep[2] += n_ - ep_t; ep_t = n_; }
+#endif
+                        if (reads_c && next_chunk && lane == 0) {
+                            // Buffer b^1 was the source of the previous chunk's store; by now
+                            // that store has long read it, so this wait is free, and the load
+                            // issued here has this chunk's arithmetic and store to land.
+                            ptx::bulk_wait_group_read<0>();
+                            ptx::mbar_arrive_expect_tx(cin_bar(ew, b ^ 1u), 4096);
+                            ptx::tma_load_2d(stg + (b ^ 1u) * 4096u, &tmap_c, cin_bar(ew, b ^ 1u),
+                                             col + kChunkCols, row0);
+                            cin_pending |= 1u << (b ^ 1u);
+                        }
                         uint8_t* row_smem = stg_ptr + b * 4096u + lane * 128u;
+                        // All eight 16-byte units of C_in are read before any result is
+                        // written back: reads and writes share the buffer, and interleaving
+                        // them would chain every unit behind the previous unit's store.
+                        uint4 cin_u[8];
+                        if (reads_c) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                cin_u[j] = *reinterpret_cast<const uint4*>(
+                                    row_smem + ((static_cast<uint32_t>(j) ^ (lane & 7u)) << 4));
+                            }
+                        }
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             OutT* unit_ptr = reinterpret_cast<OutT*>(
@@ -860,7 +931,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                 }
                             } else if (reads_c) {
                                 float cin[kUnitElems];
-                                detail::OutTraits<OutT>::load_vec(unit_ptr, cin);
+                                detail::OutTraits<OutT>::unpack(cin_u[j], cin);
 #pragma unroll
                                 for (int e = 0; e < kUnitElems; ++e) {
                                     out[e] = p.alpha * acc_f[j * kUnitElems + e] + p.beta * cin[e];
@@ -873,12 +944,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             }
                             detail::OutTraits<OutT>::store_vec(unit_ptr, out);
                         }
+#ifdef CKL_EXPERIMENT
+                        { const long long n_ = clock64(); ep[3] += n_ - ep_t; ep_t = n_; }
+#endif
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0) {
                             ptx::tma_store_2d(&tmap_c, stg + b * 4096u, col, row0);
                             ptx::bulk_commit_group();
                         }
+#ifdef CKL_EXPERIMENT
+                        ep[4] += clock64() - ep_t; 
+#endif
                     }
                 }
             } else {
@@ -920,6 +997,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             __syncwarp();
             ++seg_count;
         }
+#ifdef CKL_EXPERIMENT
+        if (p.prof && ew == 0 && lane == 0) {
+            p.prof[blockIdx.x * 8 + 2] = static_cast<unsigned long long>(ep[0]);
+            p.prof[blockIdx.x * 8 + 3] = static_cast<unsigned long long>(ep[1]);
+            p.prof[blockIdx.x * 8 + 7] = static_cast<unsigned long long>(ep[2]);
+            p.prof[blockIdx.x * 8 + 1] = static_cast<unsigned long long>(ep[3]);
+            p.prof[blockIdx.x * 8 + 4] = static_cast<unsigned long long>(ep[4]);
+        }
+#endif
         if (lane == 0) {
             // Leaving: no store may still read staging, no C_in copy may still write it.
             ptx::bulk_wait_group_read<0>();
@@ -948,13 +1034,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ptx::tmem_dealloc(tmem_base, 512);
         }
     }
-#ifdef CKL_EXPERIMENT
-    if (p.prof && threadIdx.x == 0) {
-        p.prof[blockIdx.x * 8 + 7] = ptx::global_timer_ns();  // exit (absolute)
-        p.prof[blockIdx.x * 8 + 2] = prof_entry;              // entry (absolute)
-        p.prof[blockIdx.x * 8 + 3] = prof_t0;                 // set-up done (absolute)
-    }
-#endif
 }
 
 // Fix-up pass of the stream-K split: one CTA per split tile.  Adds the FP32

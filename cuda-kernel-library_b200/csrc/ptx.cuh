@@ -183,6 +183,14 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sm
                  : "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_src), "r"(x), "r"(y)
                  : "memory");
 }
+// Pulls one box of a tensor into L2 only (no shared-memory destination, no completion
+// to wait for); x obeys the 16-byte rule.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                 :
+                 : "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y)
+                 : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
