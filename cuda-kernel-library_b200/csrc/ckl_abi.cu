@@ -234,9 +234,9 @@ Schedule make_schedule(int m, int n, int k, int mode, int max_units, int want_sk
     const long long sk_iters = static_cast<long long>(sk_tiles) * s.k_blocks;
     if (want_sk == 2) {
         // Heuristic (measured): the split pays for its partial-tile traffic and fix-up
-        // pass only when whole tiles would leave most of the machine idle and every unit
-        // still gets a long run of k blocks.
-        if (full_waves >= 1 || tiles * 4 > max_units || sk_iters / max_units < 8) {
+        // pass when whole tiles would leave a quarter or more of the machine idle and
+        // every unit still gets a long run of k blocks.
+        if (full_waves >= 1 || tiles * 4 > max_units * 3 || sk_iters / max_units < 8) {
             return s;
         }
     }
@@ -265,8 +265,13 @@ int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_al
         // The wide tile saves a quarter of the L2-to-SM traffic (higher clocks under the power
         // cap) but exposes its epilogue between tiles; measured, it wins only when the
         // main loop is long (k >= 8192) and no tile column is mostly padding.
+        auto wave_fill = [&](long long tiles) {  // share of unit-slots the last wave leaves busy
+            const long long waves = (tiles + max_pairs - 1) / max_pairs;
+            return static_cast<double>(tiles) / static_cast<double>(waves * max_pairs);
+        };
         const bool use_wide = max_pairs > 0 && wide_tiles >= max_pairs && k >= 8192 &&
-                              (n % 512 == 0 || n % 512 > 384);
+                              (n % 512 == 0 || n % 512 > 384) &&
+                              wave_fill(wide_tiles) >= wave_fill(pair_tiles) - 0.02;
         const bool use_pair = max_pairs > 0 && pair_tiles >= max_pairs;
         resolved = !legal      ? CKL_ALGO_SIMT
                    : use_wide ? CKL_ALGO_UMMA_2CTA_WIDE_SK
@@ -393,7 +398,8 @@ int launch_umma(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
     CKL_TRY_CUDA(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<kMode, OutT>, ta, tb, tc, p));
     if (p.sched.sk_tiles > 0) {
         streamk_fixup_kernel<Cfg::kTileM, Cfg::kTileN, OutT>
-            <<<p.sched.sk_tiles, 256, 0, stream>>>(p);
+            <<<dim3(static_cast<unsigned>(p.sched.sk_tiles), Cfg::kTileM / 32 * Cfg::kNHalves), 256, 0,
+               stream>>>(p);
         CKL_TRY_CUDA(cudaGetLastError());
     }
     return CKL_OK;

@@ -170,7 +170,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, 
         <<<grid, UmmaConfig<false>::kThreads, UmmaConfig<false>::kSmemBytes, stream>>>(ta, tb, tc, p);
     NOALLOC_TRY(cudaGetLastError());
     if (p.sched.sk_tiles > 0) {
-        streamk_fixup_kernel<UmmaConfig<false>::kTileM, UmmaConfig<false>::kTileN, OutT><<<p.sched.sk_tiles, 256, 0, stream>>>(p);
+        streamk_fixup_kernel<UmmaConfig<false>::kTileM, UmmaConfig<false>::kTileN, OutT><<<dim3(static_cast<unsigned>(p.sched.sk_tiles), UmmaConfig<false>::kTileM / 32), 256, 0, stream>>>(p);
         NOALLOC_TRY(cudaGetLastError());
     }
     return CKL_OK;

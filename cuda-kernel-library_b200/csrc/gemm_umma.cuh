@@ -769,9 +769,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t cin_parity = 0;
         uint32_t cin_pending = 0;  // lane 0: loads issued and not yet waited for
         const bool reads_c = (p.epi_mode == kEpiLinear) && (p.beta != 0.0f);
-#ifdef CKL_EXPERIMENT
-        long long ep[5] = {0, 0, 0, 0, 0};
-#endif
+        const bool unit_alpha = p.alpha == 1.0f;
         bool alive = true;
         while (alive && next_segment(sched, &cur, &seg)) {
             const uint32_t acc = kWide ? 0u : (seg_count & 1u);
@@ -818,9 +816,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             } else
 #endif
             if (seg.slot >= 0) {
-                // Partial accumulator -> FP32 workspace slot, full tile, no predication.
+                // Partial accumulator -> FP32 workspace slot, whole tile, no predication.  The
+                // slot is not row-major: it is the image of the registers, laid out as
+                // [32-row group][256-column half][32-column chunk][4-column unit][lane][4],
+                // so every store (and every load of the fix-up pass, which uses the same
+                // lane = row mapping) moves 512 contiguous bytes per warp.
+                const int group = row_in_tile >> 5;
                 float* dst = p.workspace + static_cast<size_t>(seg.slot) * Cfg::kSlotFloats +
-                             static_cast<size_t>(row_in_tile) * Cfg::kTileN + half * 256u;
+                             static_cast<size_t>(group * Cfg::kNHalves + static_cast<int>(half)) * 8192u +
+                             lane * 4u;
 #pragma unroll 1
                 for (int c = 0; c < 256 / 32; ++c) {
                     uint32_t r[32];
@@ -828,7 +832,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     ptx::tmem_ld_wait();
 #pragma unroll
                     for (int q = 0; q < 8; ++q) {
-                        *reinterpret_cast<uint4*>(dst + c * 32 + q * 4) =
+                        *reinterpret_cast<uint4*>(dst + c * 1024 + q * 128) =
                             make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
                     }
                 }
@@ -844,9 +848,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         }
                         const uint32_t b = static_cast<uint32_t>(c) & 1u;
                         const bool next_chunk = (c + 1 < kChunks) && (col + kChunkCols < p.n);
-#ifdef CKL_EXPERIMENT
-                        long long ep_t = clock64();
-#endif
                         if (!reads_c) {
                             // buffer b was the source of the store two chunks ago
                             if (lane == 0) {
@@ -854,9 +855,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             }
                             __syncwarp();
                         }
-#ifdef CKL_EXPERIMENT
-                        { const long long n_ = clock64(); ep[0] += n_ - ep_t; ep_t = n_; }
-#endif
                         float acc_f[kChunkCols];
 #pragma unroll
                         for (int h = 0; h < kChunkCols / 32; ++h) {
@@ -869,9 +867,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                 acc_f[h * 32 + e] = __uint_as_float(r[e]);
                             }
                         }
-#ifdef CKL_EXPERIMENT
-                        { const long long n_ = clock64(); ep[1] += n_ - ep_t; ep_t = n_; }
-#endif
                         if (reads_c) {
                             int got = 1;
                             if (lane == 0) {
@@ -892,9 +887,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             }
                             cin_parity ^= 1u << b;
                         }
-#ifdef CKL_EXPERIMENT
-                        { const long long n_ = clock64(); ep[2] += n_ - ep_t; ep_t = n_; }
-#endif
                         if (reads_c && next_chunk && lane == 0) {
                             // Buffer b^1 was the source of the previous chunk's store; by now
                             // that store has long read it, so this wait is free, and the load
@@ -932,9 +924,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             } else if (reads_c) {
                                 float cin[kUnitElems];
                                 detail::OutTraits<OutT>::unpack(cin_u[j], cin);
+                                if (unit_alpha) {
+                                    // alpha == 1 (the common case) needs no multiply; the
+                                    // product alpha*acc is exact then, so results are equal
 #pragma unroll
-                                for (int e = 0; e < kUnitElems; ++e) {
-                                    out[e] = p.alpha * acc_f[j * kUnitElems + e] + p.beta * cin[e];
+                                    for (int e = 0; e < kUnitElems; ++e) {
+                                        out[e] = fmaf(p.beta, cin[e], acc_f[j * kUnitElems + e]);
+                                    }
+                                } else {
+#pragma unroll
+                                    for (int e = 0; e < kUnitElems; ++e) {
+                                        out[e] = fmaf(p.beta, cin[e], p.alpha * acc_f[j * kUnitElems + e]);
+                                    }
                                 }
                             } else {
 #pragma unroll
@@ -944,18 +945,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             }
                             detail::OutTraits<OutT>::store_vec(unit_ptr, out);
                         }
-#ifdef CKL_EXPERIMENT
-                        { const long long n_ = clock64(); ep[3] += n_ - ep_t; ep_t = n_; }
-#endif
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0) {
                             ptx::tma_store_2d(&tmap_c, stg + b * 4096u, col, row0);
                             ptx::bulk_commit_group();
                         }
-#ifdef CKL_EXPERIMENT
-                        ep[4] += clock64() - ep_t; 
-#endif
                     }
                 }
             } else {
@@ -997,15 +992,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             __syncwarp();
             ++seg_count;
         }
-#ifdef CKL_EXPERIMENT
-        if (p.prof && ew == 0 && lane == 0) {
-            p.prof[blockIdx.x * 8 + 2] = static_cast<unsigned long long>(ep[0]);
-            p.prof[blockIdx.x * 8 + 3] = static_cast<unsigned long long>(ep[1]);
-            p.prof[blockIdx.x * 8 + 7] = static_cast<unsigned long long>(ep[2]);
-            p.prof[blockIdx.x * 8 + 1] = static_cast<unsigned long long>(ep[3]);
-            p.prof[blockIdx.x * 8 + 4] = static_cast<unsigned long long>(ep[4]);
-        }
-#endif
         if (lane == 0) {
             // Leaving: no store may still read staging, no C_in copy may still write it.
             ptx::bulk_wait_group_read<0>();
@@ -1036,16 +1022,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
 }
 
-// Fix-up pass of the stream-K split: one CTA per split tile.  Adds the FP32
-// partials of the tile in ascending unit order and applies the epilogue.
-// Tiles that a single unit covered whole were already written by the GEMM
-// kernel and are skipped.
+// Fix-up pass of the stream-K split.  Block (t, g) finishes 32 rows x 256 columns of split
+// tile t (g = row group * halves + half): it adds the FP32 partial tiles in ascending unit
+// order (so the result does not depend on timing) and applies the epilogue.  Tiles that a
+// single unit covered whole were already written by the GEMM kernel and are skipped.  The
+// partial slots hold the register image written by the GEMM epilogue: warp w of the block
+// takes 32-column chunk w, lane = row, and every load is 512 contiguous bytes per warp.
 template <int kTileM, int kTileN, typename OutT>
 __global__ void __launch_bounds__(256)
 streamk_fixup_kernel(const GemmParams p) {
     constexpr size_t kSlotFloats = static_cast<size_t>(kTileM) * kTileN;
+    constexpr int kNHalves = kTileN / 256;
     const Schedule& s = p.sched;
     const int sk_tile = static_cast<int>(blockIdx.x);
+    const int gh = static_cast<int>(blockIdx.y);  // group * kNHalves + half
 
     __shared__ int slots[kMaxFixupSlots];
     __shared__ int n_slots;
@@ -1059,39 +1049,38 @@ streamk_fixup_kernel(const GemmParams p) {
     }
     int tm, tn;
     tile_coords(s, s.dp_tiles + sk_tile, &tm, &tn);
-    OutT* c_base = static_cast<OutT*>(p.c);
-    const bool vec_ok = p.c_vec != 0;
-    // 32-column chunks: kTileM rows x 8 chunks, a warp takes 32 consecutive
-    // chunk-rows so that workspace reads are 128-byte segments per lane.
-    for (int item = static_cast<int>(threadIdx.x); item < kTileM * (kTileN / 32);
-         item += static_cast<int>(blockDim.x)) {
-        const int r = item / (kTileN / 32);
-        const int c = item % (kTileN / 32);
-        const int row = tm * kTileM + r;
-        const int col0 = tn * kTileN + c * 32;
-        if (row >= p.m || col0 >= p.n) {
-            continue;
-        }
-        float acc[32];
+    const int lane = static_cast<int>(threadIdx.x) & 31;
+    const int chunk = static_cast<int>(threadIdx.x) >> 5;  // 8 warps = 8 chunks of 32 columns
+    const int row = tm * kTileM + (gh / kNHalves) * 32 + lane;
+    const int col0 = tn * kTileN + (gh % kNHalves) * 256 + chunk * 32;
+    if (col0 >= p.n) {
+        return;  // uniform per warp
+    }
+    const float* base = p.workspace + static_cast<size_t>(gh) * 8192u + chunk * 1024 + lane * 4;
+    float acc[32];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-            acc[e] = 0.0f;
-        }
-        for (int i = 0; i < count; ++i) {
-            const float* src = p.workspace + static_cast<size_t>(slots[i]) * kSlotFloats +
-                               static_cast<size_t>(r) * kTileN + c * 32;
+    for (int e = 0; e < 32; ++e) {
+        acc[e] = 0.0f;
+    }
+    for (int i = 0; i < count; ++i) {
+        const float* src = base + static_cast<size_t>(slots[i]) * kSlotFloats;
+        float4 v[8];
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const float4 v = *reinterpret_cast<const float4*>(src + q * 4);
-                acc[4 * q] += v.x;
-                acc[4 * q + 1] += v.y;
-                acc[4 * q + 2] += v.z;
-                acc[4 * q + 3] += v.w;
-            }
+        for (int q = 0; q < 8; ++q) {
+            v[q] = __ldcg(reinterpret_cast<const float4*>(src + q * 128));
         }
-        OutT* row_ptr = c_base + static_cast<size_t>(row) * static_cast<size_t>(p.ldc);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            acc[4 * q] += v[q].x;
+            acc[4 * q + 1] += v[q].y;
+            acc[4 * q + 2] += v[q].z;
+            acc[4 * q + 3] += v[q].w;
+        }
+    }
+    if (row < p.m) {
+        OutT* row_ptr = static_cast<OutT*>(p.c) + static_cast<size_t>(row) * static_cast<size_t>(p.ldc);
         detail::finish_row_chunk<OutT>(acc, row_ptr, col0, p.n, p.alpha, p.beta, p.bias, p.epi_mode,
-                                       vec_ok);
+                                       p.c_vec != 0);
     }
 }
 
