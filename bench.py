@@ -44,8 +44,8 @@ DATASHEET_DENSE_BF16_TFLOPS = 2250.0
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0}
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the
-# ncu capture summarised in profiles/umma_gemm_kernel_pair_bf16_8192_cubed.md (1 GPU, whole problem).
-NCU_DRAM_TRAFFIC_BYTES = {"bf16_8192_cubed": 1_367_472_904}  # 1.238 GB read + 0.129 GB written
+# ncu capture summarised in profiles/umma_gemm_kernel_pairwide_bf16_8192_cubed.md (1 GPU, whole problem).
+NCU_DRAM_TRAFFIC_BYTES = {"bf16_8192_cubed": 1_233_366_568}  # 1.113 GB read + 0.121 GB written
 
 
 def load_module(name: str, path: str, search=None):
@@ -357,11 +357,11 @@ def run_ours(args) -> None:
         torch.cuda.synchronize()
         r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         r0.record()
-        for _ in range(10):
+        for _ in range(args.steps):
             torch.matmul(a, ref_b)
         r1.record()
         torch.cuda.synchronize()
-        cublas_tflops = 2.0 * M * N * K / (r0.elapsed_time(r1) / 10 * 1e-3) / 1e12
+        cublas_tflops = 2.0 * M * N * K / (r0.elapsed_time(r1) / args.steps * 1e-3) / 1e12
 
     if rank == 0:
         peaks, peak_src = measured_peaks()
@@ -376,7 +376,8 @@ def run_ours(args) -> None:
             "config": workload_config(world, ckl.algo_name(plan.algo)),
             "roofline": {
                 "bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s",
-                "frac": per_gpu / peak, "traffic": NCU_DRAM_TRAFFIC_BYTES["bf16_8192_cubed"],
+                "frac": per_gpu / peak,
+                "traffic": NCU_DRAM_TRAFFIC_BYTES["bf16_8192_cubed"] if world == 1 else None,
                 "peak_source": peak_src,
                 "flop_per_launch": 2.0 * M * w * K,
                 "frac_of_datasheet_dense_bf16": per_gpu / DATASHEET_DENSE_BF16_TFLOPS,

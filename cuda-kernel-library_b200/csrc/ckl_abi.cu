@@ -269,7 +269,7 @@ int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_al
             const long long waves = (tiles + max_pairs - 1) / max_pairs;
             return static_cast<double>(tiles) / static_cast<double>(waves * max_pairs);
         };
-        const bool use_wide = max_pairs > 0 && wide_tiles >= max_pairs && k >= 8192 &&
+        const bool use_wide = max_pairs > 0 && wide_tiles * 5 >= max_pairs * 4LL && k >= 8192 &&
                               (n % 512 == 0 || n % 512 > 384) &&
                               wave_fill(wide_tiles) >= wave_fill(pair_tiles) - 0.02;
         const bool use_pair = max_pairs > 0 && pair_tiles >= max_pairs;
