@@ -1,0 +1,133 @@
+"""Resumable benchmark sweep: run a matrix of GEMM configurations, one process each, and keep
+the rows.
+
+Counterpart of the reference's benchmarks/sweep.py:36-184.  Each configuration is one run of
+`build/bench_all gemm <variant> <dtype> <m> <n> <k> <commit>` (a separate process, so a fault in
+one configuration cannot take the sweep down); its JSON row is appended to `sweep.jsonl`, and
+`summary.csv` is rewritten from all rows.  A configuration whose key
+(family, variant, dtype, m, n, k, gpus, commit) is already in the file is skipped unless
+`--force` is given, so an interrupted sweep continues where it stopped.
+
+    python cuda-kernel-library_b200/sweep.py --out gpurun_out/sweep [--quick] [--force]
+
+The matrix holds the reference's square sizes and the benchmark configurations of this
+library's headline path (4096^3, 8192^3, the two stream-K stress shapes, one tensor-parallel
+MLP shard).
+"""
+
+from __future__ import annotations
+
+import argparse
+import csv
+import json
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+BENCH_ALL = os.path.join(HERE, "build", "bench_all")
+
+SQUARE = [512, 1024, 2048, 4096, 8192]                      # benchmarks/sweep.py:47-50 there
+SHAPES = [(4000, 3000, 5000), (1024, 1024, 32768), (16384, 1792, 4096)]
+VARIANTS = ["auto", "umma_1cta", "umma_2cta", "umma_2cta_wide", "umma_1cta_streamk"]
+DTYPES = ["fp16", "bf16", "bf16_c16"]
+FIELDS = ["family", "variant", "dtype", "m", "n", "k", "gpus", "median_ms", "iqr_ms", "gflops",
+          "tflops", "pct_peak_datasheet", "baseline_gflops", "pct_baseline", "median_sm_clock_mhz",
+          "max_temp_c", "max_power_w", "throttled", "power_capped", "commit"]
+
+
+def matrix(quick: bool):
+    sizes = [(s, s, s) for s in (SQUARE[:3] if quick else SQUARE)]
+    shapes = sizes + ([] if quick else SHAPES)
+    for variant in (VARIANTS[:2] if quick else VARIANTS):
+        for dtype in (DTYPES[:1] if quick else DTYPES):
+            for m, n, k in shapes:
+                yield {"family": "gemm", "variant": variant, "dtype": dtype, "m": m, "n": n, "k": k,
+                       "gpus": 1}
+
+
+def key_of(row: dict) -> tuple:
+    return tuple(row.get(f) for f in ("family", "variant", "dtype", "m", "n", "k", "gpus", "commit"))
+
+
+def load_rows(path: str) -> list[dict]:
+    rows = []
+    if os.path.exists(path):
+        with open(path) as f:
+            for line in f:
+                line = line.strip()
+                if line:
+                    rows.append(json.loads(line))
+    return rows
+
+
+def write_summary(rows: list[dict], path: str) -> None:
+    with open(path, "w", newline="") as f:
+        w = csv.DictWriter(f, fieldnames=FIELDS, extrasaction="ignore")
+        w.writeheader()
+        for row in sorted(rows, key=lambda r: (r["variant"], r["dtype"], r["m"], r["n"], r["k"])):
+            w.writerow(row)
+
+
+def current_commit() -> str:
+    try:
+        return subprocess.run(["git", "-C", ROOT, "rev-parse", "--short", "HEAD"], check=True,
+                              capture_output=True, text=True).stdout.strip()
+    except Exception:
+        return "unknown"
+
+
+def run_one(cfg: dict, commit: str, runner=None) -> dict | None:
+    """Runs one configuration in its own process; returns the parsed row or None."""
+    cmd = [BENCH_ALL, "gemm", cfg["variant"], cfg["dtype"], str(cfg["m"]), str(cfg["n"]),
+           str(cfg["k"]), commit]
+    env = dict(os.environ, CKL_REPO_ROOT=ROOT)
+    proc = (runner or subprocess.run)(cmd, capture_output=True, text=True, env=env, timeout=600)
+    if proc.returncode != 0:
+        sys.stderr.write(f"[sweep] {' '.join(cmd[1:])} failed ({proc.returncode}): "
+                         f"{proc.stderr.strip()[-300:]}\n")
+        return None
+    return json.loads(proc.stdout.strip().splitlines()[-1])
+
+
+def sweep(out_dir: str, quick: bool = False, force: bool = False, commit: str | None = None,
+          runner=None) -> tuple[int, int]:
+    """Returns (configurations run, configurations skipped as already done)."""
+    os.makedirs(out_dir, exist_ok=True)
+    jsonl = os.path.join(out_dir, "sweep.jsonl")
+    commit = commit or current_commit()
+    rows = load_rows(jsonl)
+    done = {key_of(r) for r in rows}
+    ran = skipped = 0
+    for cfg in matrix(quick):
+        if not force and key_of(dict(cfg, commit=commit)) in done:
+            skipped += 1
+            continue
+        row = run_one(cfg, commit, runner)
+        if row is None:
+            continue
+        rows.append(row)
+        done.add(key_of(row))
+        with open(jsonl, "a") as f:
+            f.write(json.dumps(row) + "\n")
+        write_summary(rows, os.path.join(out_dir, "summary.csv"))
+        ran += 1
+    write_summary(rows, os.path.join(out_dir, "summary.csv"))
+    return ran, skipped
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "sweep"))
+    ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--force", action="store_true")
+    args = ap.parse_args()
+    if not os.path.exists(BENCH_ALL):
+        raise SystemExit(f"{BENCH_ALL} is missing: run `make -C {os.path.join(HERE, 'tools')}`")
+    ran, skipped = sweep(args.out, args.quick, args.force)
+    print(f"[sweep] ran {ran}, skipped {skipped} already present; results in {args.out}")
+
+
+if __name__ == "__main__":
+    main()

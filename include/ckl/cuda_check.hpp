@@ -1,48 +1,36 @@
 #pragma once
-// Error checking for CUDA runtime calls made by tests, benchmarks and tools.
-// Same macro names and the same behaviour (throw std::runtime_error naming
-// the failing expression and its location) as the reference's
-// include/ckl/cuda_check.hpp:35-47, so harness code written against it
-// compiles here unchanged.
+// CKL_CUDA_CHECK / CKL_CUDA_LAST_ERROR for harness code (tests, benchmarks, tools).
+// Names and behaviour follow the reference's include/ckl/cuda_check.hpp:35-47: a failing
+// runtime call becomes a std::runtime_error that names the call and where it was made.
 
+#include <sstream>
 #include <stdexcept>
-#include <string>
 
 #include <cuda_runtime.h>
 
 namespace ckl {
 
-inline void check_cuda(cudaError_t status, const char* expr, const char* file, int line) {
-    if (status == cudaSuccess) {
-        return;
-    }
-    std::string text = "CUDA error ";
-    text += cudaGetErrorName(status);
-    text += " (";
-    text += cudaGetErrorString(status);
-    text += "): ";
-    text += expr;
-    text += " at ";
-    text += file;
-    text += ":";
-    text += std::to_string(line);
-    throw std::runtime_error(text);
+[[noreturn]] inline void fail(const char* what, const char* expr, const char* file, int line) {
+    std::ostringstream os;
+    os << what << " failed: " << expr << " at " << file << ':' << line;
+    throw std::runtime_error(os.str());
 }
 
-[[noreturn]] inline void fail(const char* what, const char* expr, const char* file, int line) {
-    throw std::runtime_error(std::string(what) + " failed: " + expr + " at " + file + ":" +
-                             std::to_string(line));
+inline void check_cuda(cudaError_t status, const char* expr, const char* file, int line) {
+    if (status != cudaSuccess) {
+        std::ostringstream os;
+        os << "CUDA error " << cudaGetErrorName(status) << " (" << cudaGetErrorString(status)
+           << "): " << expr << " at " << file << ':' << line;
+        throw std::runtime_error(os.str());
+    }
+}
+
+inline void check_last_error(bool also_sync, const char* file, int line) {
+    check_cuda(cudaGetLastError(), "kernel launch", file, line);
+    if (also_sync) check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize", file, line);
 }
 
 }  // namespace ckl
 
 #define CKL_CUDA_CHECK(expr) ::ckl::check_cuda((expr), #expr, __FILE__, __LINE__)
-
-#define CKL_CUDA_LAST_ERROR(sync)                                                          \
-    do {                                                                                   \
-        ::ckl::check_cuda(cudaGetLastError(), "kernel launch", __FILE__, __LINE__);        \
-        if (sync) {                                                                        \
-            ::ckl::check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize", __FILE__,  \
-                              __LINE__);                                                   \
-        }                                                                                  \
-    } while (0)
+#define CKL_CUDA_LAST_ERROR(sync) ::ckl::check_last_error((sync), __FILE__, __LINE__)

@@ -1,10 +1,10 @@
 #pragma once
-// Move-only owner of a device allocation, for tests and benchmarks.  Interface
-// of the reference's include/ckl/device_buffer.hpp:18-88 (data, size, bytes,
-// copy_from_host, copy_to_host, to_host, zero); copies are synchronous.
+// DeviceBuffer<T>: test/benchmark helper that owns `size()` elements of device memory.
+// Interface of the reference's include/ckl/device_buffer.hpp:18-88 so its drivers compile
+// unchanged; built here on std::unique_ptr with a cudaFree deleter.  All copies block.
 
 #include <cstddef>
-#include <utility>
+#include <memory>
 #include <vector>
 
 #include <cuda_runtime.h>
@@ -13,64 +13,59 @@
 
 namespace ckl {
 
+namespace detail {
+struct CudaFreeDeleter {
+    void operator()(void* p) const noexcept {
+        if (p) cudaFree(p);
+    }
+};
+inline std::unique_ptr<void, CudaFreeDeleter> device_alloc(std::size_t nbytes) {
+    void* raw = nullptr;
+    if (nbytes) CKL_CUDA_CHECK(cudaMalloc(&raw, nbytes));
+    return std::unique_ptr<void, CudaFreeDeleter>(raw);
+}
+}  // namespace detail
+
 template <typename T>
 class DeviceBuffer {
+    std::unique_ptr<void, detail::CudaFreeDeleter> mem_;
+    std::size_t elems_ = 0;
+
 public:
     DeviceBuffer() = default;
-    explicit DeviceBuffer(std::size_t count) : n_(count) {
-        if (n_ != 0) {
-            CKL_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&p_), n_ * sizeof(T)));
-        }
+    explicit DeviceBuffer(std::size_t count)
+        : mem_(detail::device_alloc(count * sizeof(T))), elems_(count) {}
+    DeviceBuffer(DeviceBuffer&& other) noexcept
+        : mem_(std::move(other.mem_)), elems_(other.elems_) {
+        other.elems_ = 0;
     }
-    DeviceBuffer(const DeviceBuffer&) = delete;
-    DeviceBuffer& operator=(const DeviceBuffer&) = delete;
-    DeviceBuffer(DeviceBuffer&& o) noexcept { swap(o); }
-    DeviceBuffer& operator=(DeviceBuffer&& o) noexcept {
-        if (this != &o) {
-            release();
-            swap(o);
-        }
+    DeviceBuffer& operator=(DeviceBuffer&& other) noexcept {
+        mem_ = std::move(other.mem_);
+        elems_ = other.elems_;
+        other.elems_ = 0;
         return *this;
     }
-    ~DeviceBuffer() { release(); }
 
-    T* data() { return p_; }
-    const T* data() const { return p_; }
-    std::size_t size() const { return n_; }
-    std::size_t bytes() const { return n_ * sizeof(T); }
+    std::size_t size() const { return elems_; }
+    std::size_t bytes() const { return sizeof(T) * elems_; }
+    T* data() { return static_cast<T*>(mem_.get()); }
+    const T* data() const { return static_cast<const T*>(mem_.get()); }
 
-    void copy_from_host(const T* host, std::size_t count) {
-        CKL_CUDA_CHECK(cudaMemcpy(p_, host, count * sizeof(T), cudaMemcpyHostToDevice));
+    void zero() {
+        if (elems_) CKL_CUDA_CHECK(cudaMemset(mem_.get(), 0, bytes()));
     }
-    void copy_from_host(const std::vector<T>& host) { copy_from_host(host.data(), host.size()); }
-    void copy_to_host(T* host, std::size_t count) const {
-        CKL_CUDA_CHECK(cudaMemcpy(host, p_, count * sizeof(T), cudaMemcpyDeviceToHost));
+    void copy_from_host(const T* src, std::size_t count) {
+        CKL_CUDA_CHECK(cudaMemcpy(mem_.get(), src, sizeof(T) * count, cudaMemcpyHostToDevice));
+    }
+    void copy_from_host(const std::vector<T>& src) { copy_from_host(src.data(), src.size()); }
+    void copy_to_host(T* dst, std::size_t count) const {
+        CKL_CUDA_CHECK(cudaMemcpy(dst, mem_.get(), sizeof(T) * count, cudaMemcpyDeviceToHost));
     }
     std::vector<T> to_host() const {
-        std::vector<T> out(n_);
-        copy_to_host(out.data(), n_);
-        return out;
+        std::vector<T> host(elems_);
+        if (elems_) copy_to_host(host.data(), elems_);
+        return host;
     }
-    void zero() {
-        if (n_ != 0) {
-            CKL_CUDA_CHECK(cudaMemset(p_, 0, bytes()));
-        }
-    }
-
-private:
-    void swap(DeviceBuffer& o) noexcept {
-        std::swap(p_, o.p_);
-        std::swap(n_, o.n_);
-    }
-    void release() noexcept {
-        if (p_ != nullptr) {
-            cudaFree(p_);
-        }
-        p_ = nullptr;
-        n_ = 0;
-    }
-    T* p_ = nullptr;
-    std::size_t n_ = 0;
 };
 
 }  // namespace ckl

@@ -130,3 +130,37 @@ def test_restatement_equals_reference_build(orc, oracle_mod):
         assert np.array_equal(c1, c2)
         x = c1.astype(np.float32) + np.float32(1e-4)
         assert orc.relative_frobenius_error(x, c1) == ref.relative_frobenius_error(x, c2)
+
+
+def test_cpp_harness_header_matches_golden(tmp_path, orc):
+    """include/ckl/reference.hpp (used by the C++ drivers) produces the reference's values."""
+    import shutil
+    import subprocess
+    if shutil.which("g++") is None:
+        pytest.skip("g++ not available")
+    root = os.path.dirname(HERE)
+    src = tmp_path / "probe.cpp"
+    src.write_text(r'''
+#include <cstdio>
+#include "ckl/reference.hpp"
+int main() {
+    const int m = 129, n = 257, k = 193;
+    auto a = ckl::random_matrix(m, k, 0x1111 + m);
+    auto b = ckl::random_matrix(k, n, 0x2222 + n);
+    std::vector<float> c0(static_cast<size_t>(m) * n, 0.0f);
+    auto c = ckl::gemm_reference(a, b, c0, m, n, k, 1.0f, 0.0f);
+    std::FILE* f = std::fopen("c.bin", "wb");
+    std::fwrite(c.data(), sizeof(double), c.size(), f);
+    std::fclose(f);
+    std::vector<float> cf(c.begin(), c.end());
+    std::printf("%.17g\n", ckl::relative_frobenius_error(cf, c));
+}
+''')
+    exe = tmp_path / "probe"
+    subprocess.run(["g++", "-O2", "-std=c++17", "-I", os.path.join(root, "include"), str(src), "-o",
+                    str(exe)], check=True)
+    subprocess.run([str(exe)], check=True, cwd=tmp_path, capture_output=True)
+    c = np.fromfile(tmp_path / "c.bin", dtype=np.float64)
+    gold = next(e for e in GOLD["gemm_reference"]
+                if (e["m"], e["n"], e["k"], e["beta"]) == (129, 257, 193, 0.0))
+    assert sha(c) == gold["sha256"]
