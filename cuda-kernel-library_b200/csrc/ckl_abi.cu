@@ -858,7 +858,7 @@ int ckl_stream_copy(void* dst, const void* src, size_t bytes, ckl_stream_t strea
     if (const int rc = get_ctx(&ctx); rc != CKL_OK) {
         return rc;
     }
-    stream_copy_kernel<<<ctx->sm_count * 4, 512, 0, static_cast<cudaStream_t>(stream)>>>(
+    stream_copy_kernel<<<ctx->sm_count * 2, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<uint4*>(dst), static_cast<const uint4*>(src), bytes / 16);
     CKL_TRY_CUDA(cudaGetLastError());
     return CKL_OK;

@@ -183,24 +183,31 @@ __global__ void assemble_column_blocks_kernel(T* __restrict__ dst, const T* __re
     }
 }
 
-// Bandwidth probe: grid-stride 16-byte copy with four independent loads in
-// flight per thread (HBM3e needs far more bytes in flight per SM than the
-// reference's one-load-per-iteration loop, src/tools/device_probe.cu:25-31).
-__global__ void __launch_bounds__(512)
+// Bandwidth probe: each thread moves eight 16-byte words per trip, all eight loads issued
+// before the first store, with streaming (evict-first) hints on both sides.  HBM3e needs far
+// more bytes in flight per SM than the reference's one-load-per-iteration loop provides
+// (src/tools/device_probe.cu:25-31 there).
+__global__ void __launch_bounds__(1024)
 stream_copy_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, size_t count) {
-    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-    size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    for (; i + 3 * stride < count; i += 4 * stride) {
-        const uint4 v0 = src[i];
-        const uint4 v1 = src[i + stride];
-        const uint4 v2 = src[i + 2 * stride];
-        const uint4 v3 = src[i + 3 * stride];
-        dst[i] = v0;
-        dst[i + stride] = v1;
-        dst[i + 2 * stride] = v2;
-        dst[i + 3 * stride] = v3;
+    // A block copies contiguous 128 KB pieces (8 x 1024 x 16 B), pieces dealt round-robin to
+    // blocks: consecutive lines of a DRAM page are touched together.
+    constexpr int kUnroll = 8;
+    const size_t piece = static_cast<size_t>(kUnroll) * blockDim.x;
+    const size_t pieces = count / piece;
+    for (size_t t = blockIdx.x; t < pieces; t += gridDim.x) {
+        const size_t base = t * piece + threadIdx.x;
+        uint4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            v[u] = __ldcs(src + base + static_cast<size_t>(u) * blockDim.x);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            __stcs(dst + base + static_cast<size_t>(u) * blockDim.x, v[u]);
+        }
     }
-    for (; i < count; i += stride) {
+    for (size_t i = pieces * piece + static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+         i < count; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
         dst[i] = src[i];
     }
 }
