@@ -678,12 +678,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         }
                     }
                     if constexpr (kPair) {
-#ifdef CKL_PAIR_MCAST_COMMIT
-                        ptx::umma_commit_pair_both(empty_bar(stage));
-#else
                         ptx::umma_commit_pair(empty_bar(stage));
                         ptx::umma_commit_pair(ptx::map_to_cta(empty_bar(stage), 1));
-#endif
                     } else {
                         ptx::umma_commit(empty_bar(stage));
                     }
@@ -701,12 +697,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #endif
                 if (ok) {
                     if constexpr (kPair) {
-#ifdef CKL_PAIR_MCAST_COMMIT
-                        ptx::umma_commit_pair_both(acc_full_bar(acc));
-#else
                         ptx::umma_commit_pair(acc_full_bar(acc));
                         ptx::umma_commit_pair(ptx::map_to_cta(acc_full_bar(acc), 1));
-#endif
                     } else {
                         ptx::umma_commit(acc_full_bar(acc));
                     }

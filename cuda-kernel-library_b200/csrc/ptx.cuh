@@ -283,18 +283,6 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
                  : "memory");
 }
 
-#ifdef CKL_PAIR_MCAST_COMMIT
-// Pair form signalling the barrier at the same offset in both CTAs of the pair.
-__device__ __forceinline__ void umma_commit_pair_both(uint32_t bar) {
-    asm volatile(
-        "{\n\t"
-        ".reg .b16 m;\n\t"
-        "mov.b16 m, 3;\n\t"
-        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t"
-        "}" ::"r"(bar)
-        : "memory");
-}
-#endif
 
 // ---- tcgen05.ld -------------------------------------------------------------
 
