@@ -217,6 +217,10 @@ struct OutTraits<float> {
         v[0] = __uint_as_float(t.x); v[1] = __uint_as_float(t.y);
         v[2] = __uint_as_float(t.z); v[3] = __uint_as_float(t.w);
     }
+    // Element e (a compile-time constant after unrolling) of a 16-byte unit.
+    static __device__ __forceinline__ float element(const uint4& t, int e) {
+        return __uint_as_float(e == 0 ? t.x : e == 1 ? t.y : e == 2 ? t.z : t.w);
+    }
 };
 template <>
 struct OutTraits<__half> {
@@ -241,6 +245,11 @@ struct OutTraits<__half> {
             v[2 * i] = f.x;
             v[2 * i + 1] = f.y;
         }
+    }
+    static __device__ __forceinline__ float element(const uint4& t, int e) {
+        const uint32_t w = (e >> 1) == 0 ? t.x : (e >> 1) == 1 ? t.y : (e >> 1) == 2 ? t.z : t.w;
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+        return (e & 1) ? f.y : f.x;
     }
     static __device__ __forceinline__ void store_vec(__half* p, const float* v) {
         uint4 t;
@@ -279,6 +288,11 @@ struct OutTraits<__nv_bfloat16> {
             v[2 * i] = f.x;
             v[2 * i + 1] = f.y;
         }
+    }
+    static __device__ __forceinline__ float element(const uint4& t, int e) {
+        // BF16 is the upper half of an FP32 word
+        const uint32_t w = (e >> 1) == 0 ? t.x : (e >> 1) == 1 ? t.y : (e >> 1) == 2 ? t.z : t.w;
+        return __uint_as_float((e & 1) ? (w & 0xffff0000u) : (w << 16));
     }
     static __device__ __forceinline__ void store_vec(__nv_bfloat16* p, const float* v) {
         uint4 t;
@@ -763,6 +777,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const bool reads_c = (p.epi_mode == kEpiLinear) && (p.beta != 0.0f);
         const bool unit_alpha = p.alpha == 1.0f;
         bool alive = true;
+#ifdef CKL_EXPERIMENT
+        long long ep_ld = 0, ep_cw = 0, ep_ci = 0, ep_cp = 0, ep_st = 0, ep_t = 0;
+#define CKL_EP(acc_) do { const long long n_ = clock64(); acc_ += n_ - ep_t; ep_t = n_; } while (0)
+#else
+#define CKL_EP(acc_) do { } while (0)
+#endif
         while (alive && next_segment(sched, &cur, &seg)) {
             const uint32_t acc = kWide ? 0u : (seg_count & 1u);
             const uint32_t acc_parity = kWide ? (seg_count & 1u) : ((seg_count >> 1) & 1u);
@@ -778,11 +798,41 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const bool tma_path = (p.c_tma != 0) && seg.slot < 0;
             const bool warp_has_rows = row0 < p.m;
 
-            // C_in of the first chunk can be fetched before the accumulator is ready.
-            if (tma_path && reads_c && warp_has_rows && lane == 0) {
-                ptx::mbar_arrive_expect_tx(cin_bar(ew, 0), 4096);
-                ptx::tma_load_2d(stg, &tmap_c, cin_bar(ew, 0), col_base, row0);
-                cin_pending |= 1u;
+            // Hands the accumulator back to the MMA warp, once per tile: called as soon as
+            // the last TMEM load of the tile has completed.
+            bool released = false;
+            auto release_acc = [&]() {
+                if (released) {
+                    return;
+                }
+                released = true;
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    const int release = static_cast<int>(kWide ? half : acc);
+                    if constexpr (kPair) {
+                        ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_empty_bar(release), 0));
+                    } else {
+                        ptx::mbar_arrive(acc_empty_bar(release));
+                    }
+                }
+            };
+
+            // Chunks of kChunkCols columns this warp writes through the TMA path.
+            const int cols_left = p.n - col_base;
+            const int n_chunks =
+                !tma_path || !warp_has_rows || cols_left <= 0
+                    ? 0
+                    : (cols_left >= 256 ? kChunks : (cols_left + kChunkCols - 1) / kChunkCols);
+            // C_in of the first two chunks is fetched before the accumulator is ready: both
+            // staging buffers are idle until then.
+            if (reads_c && lane == 0) {
+                for (int c = 0; c < 2 && c < n_chunks; ++c) {
+                    ptx::mbar_arrive_expect_tx(cin_bar(ew, c), 4096);
+                    ptx::tma_load_2d(stg + static_cast<uint32_t>(c) * 4096u, &tmap_c, cin_bar(ew, c),
+                                     col_base + c * kChunkCols, row0);
+                    cin_pending |= 1u << c;
+                }
             }
 
             int ok = 1;
@@ -829,121 +879,134 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     }
                 }
             } else if (tma_path) {
-                // Coalesced path: registers -> swizzled staging -> TMA store (and C_in
-                // arrives by TMA load into the same buffer, one chunk ahead).
-                if (warp_has_rows) {
-#pragma unroll 1
-                    for (int c = 0; c < kChunks; ++c) {
-                        const int col = col_base + c * kChunkCols;
-                        if (col >= p.n) {
-                            break;  // uniform
-                        }
-                        const uint32_t b = static_cast<uint32_t>(c) & 1u;
-                        const bool next_chunk = (c + 1 < kChunks) && (col + kChunkCols < p.n);
-                        if (!reads_c) {
-                            // buffer b was the source of the store two chunks ago
-                            if (lane == 0) {
-                                ptx::bulk_wait_group_read<1>();
-                            }
-                            __syncwarp();
-                        }
-                        float acc_f[kChunkCols];
+                // Coalesced path: registers -> swizzled staging -> TMA store; C_in arrives by
+                // TMA load into the same buffer.  The accumulator goes back to the MMA warp as
+                // soon as its last columns are in registers.
+                auto load_acc = [&](int c, uint32_t (&dst)[kChunkCols]) {
 #pragma unroll
-                        for (int h = 0; h < kChunkCols / 32; ++h) {
-                            uint32_t r[32];
-                            ptx::tmem_ld_32x32(
-                                t_row + static_cast<uint32_t>(c * kChunkCols + h * 32), r);
-                            ptx::tmem_ld_wait();
-#pragma unroll
-                            for (int e = 0; e < 32; ++e) {
-                                acc_f[h * 32 + e] = __uint_as_float(r[e]);
-                            }
+                    for (int h = 0; h < kChunkCols / 32; ++h) {
+                        ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(c * kChunkCols + h * 32),
+                                           *reinterpret_cast<uint32_t(*)[32]>(dst + h * 32));
+                    }
+                };
+                // One chunk: `r` holds its accumulator columns (already waited for).
+                auto finish_chunk = [&](int c, uint32_t (&r)[kChunkCols]) -> bool {
+                    const int col = col_base + c * kChunkCols;
+                    const uint32_t b = static_cast<uint32_t>(c) & 1u;
+                    if (!reads_c) {
+                        // buffer b was the source of the store two chunks ago
+                        if (lane == 0) {
+                            ptx::bulk_wait_group_read<1>();
                         }
-                        if (reads_c) {
-                            int got = 1;
-                            if (lane == 0) {
-                                got = detail::wait_barrier(cin_bar(ew, b), (cin_parity >> b) & 1u,
-                                                           ctl, kRoleEpilogue, 0x40000000u | seg_count)
-                                          ? 1
-                                          : 0;
-                                cin_pending &= ~(1u << b);
-                            }
-                            got = __shfl_sync(0xFFFFFFFFu, got, 0);
-                            if (!got) {
-                                alive = false;
-                                break;
-                            }
-                            for (int i = 0;
-                                 i < 1024 && !ptx::mbar_try_wait(cin_bar(ew, b), (cin_parity >> b) & 1u);
-                                 ++i) {
-                            }
-                            cin_parity ^= 1u << b;
+                        __syncwarp();
+                    } else {
+                        int got = 1;
+                        if (lane == 0) {
+                            got = detail::wait_barrier(cin_bar(ew, b), (cin_parity >> b) & 1u, ctl,
+                                                       kRoleEpilogue, 0x40000000u | seg_count)
+                                      ? 1
+                                      : 0;
+                            cin_pending &= ~(1u << b);
                         }
-                        if (reads_c && next_chunk && lane == 0) {
-                            // Buffer b^1 was the source of the previous chunk's store; by now
-                            // that store has long read it, so this wait is free, and the load
-                            // issued here has this chunk's arithmetic and store to land.
-                            ptx::bulk_wait_group_read<0>();
-                            ptx::mbar_arrive_expect_tx(cin_bar(ew, b ^ 1u), 4096);
-                            ptx::tma_load_2d(stg + (b ^ 1u) * 4096u, &tmap_c, cin_bar(ew, b ^ 1u),
-                                             col + kChunkCols, row0);
-                            cin_pending |= 1u << (b ^ 1u);
+                        got = __shfl_sync(0xFFFFFFFFu, got, 0);
+                        if (!got) {
+                            return false;
                         }
-                        uint8_t* row_smem = stg_ptr + b * 4096u + lane * 128u;
-                        // All eight 16-byte units of C_in are read before any result is
-                        // written back: reads and writes share the buffer, and interleaving
-                        // them would chain every unit behind the previous unit's store.
-                        uint4 cin_u[8];
-                        if (reads_c) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                cin_u[j] = *reinterpret_cast<const uint4*>(
-                                    row_smem + ((static_cast<uint32_t>(j) ^ (lane & 7u)) << 4));
-                            }
+                        for (int i = 0;
+                             i < 1024 && !ptx::mbar_try_wait(cin_bar(ew, b), (cin_parity >> b) & 1u); ++i) {
                         }
+                        cin_parity ^= 1u << b;
+                    }
+                    CKL_EP(ep_cw);
+                    if (reads_c && c >= 1 && c + 1 < n_chunks && lane == 0) {
+                        // Buffer b^1 was the source of the previous chunk's store; once that
+                        // store has read it, the C_in of the next chunk can land there.
+                        ptx::bulk_wait_group_read<0>();
+                        ptx::mbar_arrive_expect_tx(cin_bar(ew, b ^ 1u), 4096);
+                        ptx::tma_load_2d(stg + (b ^ 1u) * 4096u, &tmap_c, cin_bar(ew, b ^ 1u),
+                                         col + kChunkCols, row0);
+                        cin_pending |= 1u << (b ^ 1u);
+                    }
+                    CKL_EP(ep_ci);
+                    uint8_t* row_smem = stg_ptr + b * 4096u + lane * 128u;
+                    // All eight 16-byte units of C_in are read before any result is written
+                    // back: reads and writes share the buffer, and interleaving them would
+                    // chain every unit behind the previous unit's store.
+                    uint4 cin_u[8];
+                    if (reads_c) {
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            OutT* unit_ptr = reinterpret_cast<OutT*>(
+                            cin_u[j] = *reinterpret_cast<const uint4*>(
                                 row_smem + ((static_cast<uint32_t>(j) ^ (lane & 7u)) << 4));
-                            float out[kUnitElems];
-                            if (p.epi_mode == kEpiBiasRelu) {
-#pragma unroll
-                                for (int e = 0; e < kUnitElems; ++e) {
-                                    const int gc = col + j * kUnitElems + e;
-                                    const float bv = gc < p.n ? __ldg(p.bias + gc) : 0.0f;
-                                    out[e] = fmaxf(p.alpha * acc_f[j * kUnitElems + e] + bv, 0.0f);
-                                }
-                            } else if (reads_c) {
-                                float cin[kUnitElems];
-                                detail::OutTraits<OutT>::unpack(cin_u[j], cin);
-                                if (unit_alpha) {
-                                    // alpha == 1 (the common case) needs no multiply; the
-                                    // product alpha*acc is exact then, so results are equal
-#pragma unroll
-                                    for (int e = 0; e < kUnitElems; ++e) {
-                                        out[e] = fmaf(p.beta, cin[e], acc_f[j * kUnitElems + e]);
-                                    }
-                                } else {
-#pragma unroll
-                                    for (int e = 0; e < kUnitElems; ++e) {
-                                        out[e] = fmaf(p.beta, cin[e], p.alpha * acc_f[j * kUnitElems + e]);
-                                    }
-                                }
-                            } else {
-#pragma unroll
-                                for (int e = 0; e < kUnitElems; ++e) {
-                                    out[e] = p.alpha * acc_f[j * kUnitElems + e];
-                                }
-                            }
-                            detail::OutTraits<OutT>::store_vec(unit_ptr, out);
-                        }
-                        ptx::fence_proxy_async_smem();
-                        __syncwarp();
-                        if (lane == 0) {
-                            ptx::tma_store_2d(&tmap_c, stg + b * 4096u, col, row0);
-                            ptx::bulk_commit_group();
                         }
                     }
+                    // One straight-line loop per epilogue flavour: a flavour test inside the
+                    // loop would cut it into eight blocks the compiler cannot overlap.
+                    auto emit = [&](auto&& value_of) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            float out[kUnitElems];
+#pragma unroll
+                            for (int e = 0; e < kUnitElems; ++e) {
+                                out[e] = value_of(j, e);
+                            }
+                            detail::OutTraits<OutT>::store_vec(
+                                reinterpret_cast<OutT*>(
+                                    row_smem + ((static_cast<uint32_t>(j) ^ (lane & 7u)) << 4)),
+                                out);
+                        }
+                    };
+                    auto acc_of = [&](int j, int e) { return __uint_as_float(r[j * kUnitElems + e]); };
+                    auto cin = [&](int j, int e) {
+                        return detail::OutTraits<OutT>::element(cin_u[j], e);
+                    };
+                    if (p.epi_mode == kEpiBiasRelu) {
+                        emit([&](int j, int e) {
+                            const int gc = col + j * kUnitElems + e;
+                            const float bv = gc < p.n ? __ldg(p.bias + gc) : 0.0f;
+                            return fmaxf(p.alpha * acc_of(j, e) + bv, 0.0f);
+                        });
+                    } else if (reads_c) {
+                        if (unit_alpha) {
+                            // alpha == 1 (the common case) needs no multiply; the product
+                            // alpha*acc is exact then, so the results are the same
+                            emit([&](int j, int e) { return fmaf(p.beta, cin(j, e), acc_of(j, e)); });
+                        } else {
+                            emit([&](int j, int e) {
+                                return fmaf(p.beta, cin(j, e), p.alpha * acc_of(j, e));
+                            });
+                        }
+                    } else if (unit_alpha) {
+                        emit([&](int j, int e) { return acc_of(j, e); });
+                    } else {
+                        emit([&](int j, int e) { return p.alpha * acc_of(j, e); });
+                    }
+                    CKL_EP(ep_cp);
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::tma_store_2d(&tmap_c, stg + b * 4096u, col, row0);
+                        ptx::bulk_commit_group();
+                    }
+                    CKL_EP(ep_st);
+                    return true;
+                };
+#pragma unroll 1
+                for (int c = 0; c < n_chunks && alive; ++c) {
+#ifdef CKL_EXPERIMENT
+                    ep_t = clock64();
+#endif
+                    uint32_t r[kChunkCols];
+                    load_acc(c, r);
+                    ptx::tmem_ld_wait();
+                    if (c + 1 == n_chunks) {
+                        release_acc();  // the last columns are in registers
+                    }
+                    CKL_EP(ep_ld);
+                    alive = finish_chunk(c, r);
+                }
+                if (!alive) {
+                    break;
                 }
             } else {
                 OutT* row_ptr = c_base + static_cast<size_t>(row) * static_cast<size_t>(p.ldc);
@@ -968,22 +1031,22 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
             }
             // All TMEM reads of this accumulator are done: hand it back to the MMA warp.
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-                const int release = static_cast<int>(kWide ? half : acc);
-                if constexpr (kPair) {
-                    ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_empty_bar(release), 0));
-                } else {
-                    ptx::mbar_arrive(acc_empty_bar(release));
-                }
-                if (tma_path) {
-                    ptx::bulk_wait_group_read<0>();  // staging is reusable by the next tile
-                }
+            release_acc();
+            if (lane == 0 && tma_path) {
+                ptx::bulk_wait_group_read<0>();  // staging is reusable by the next tile
             }
             __syncwarp();
             ++seg_count;
         }
+#ifdef CKL_EXPERIMENT
+        if (p.prof && ew == 0 && lane == 0) {
+            p.prof[blockIdx.x * 8 + 1] = static_cast<unsigned long long>(ep_ld);
+            p.prof[blockIdx.x * 8 + 2] = static_cast<unsigned long long>(ep_cw);
+            p.prof[blockIdx.x * 8 + 3] = static_cast<unsigned long long>(ep_ci);
+            p.prof[blockIdx.x * 8 + 4] = static_cast<unsigned long long>(ep_cp);
+            p.prof[blockIdx.x * 8 + 7] = static_cast<unsigned long long>(ep_st);
+        }
+#endif
         if (lane == 0) {
             // Leaving: no store may still read staging, no C_in copy may still write it.
             ptx::bulk_wait_group_read<0>();

@@ -56,8 +56,15 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // Arrive on a barrier that may live in the peer CTA of the cluster (address in
 // the shared::cluster window, from mapa).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+#if defined(CKL_ARRIVE_CLUSTER_RELEASE)
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
                  : "memory");
+#else
+    // Default semantics (release at CTA scope).  The arrivals made with this publish no
+    // ordinary memory: a drained accumulator is ordered by tcgen05.fence, so the far more
+    // expensive cluster-scope release is not needed.
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+#endif
 }
 
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
