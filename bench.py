@@ -45,7 +45,7 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0}
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the
 # ncu capture summarised in profiles/umma_gemm_kernel_pairwide_bf16_8192_cubed.md (1 GPU, whole problem).
-NCU_DRAM_TRAFFIC_BYTES = {"bf16_8192_cubed": 1_233_366_568}  # 1.113 GB read + 0.121 GB written
+NCU_DRAM_TRAFFIC_BYTES = {"bf16_8192_cubed": 1_233_121_168}  # 1.112922 GB read + 0.120199 GB written
 
 
 def load_module(name: str, path: str, search=None):
