@@ -64,6 +64,8 @@ _lib.ckl_gemm_bias_relu_ex.argtypes = [_i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _
                                        _vp]
 _lib.ckl_bias_relu_f32.argtypes = [_vp, _vp, _i, _i, _i, _vp]
 _lib.ckl_gemm_host.argtypes = [_i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f]
+_lib.ckl_sgemm.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp]
+_lib.ckl_strsm_lower.argtypes = [_vp, _vp, _i, _i, _i, _i, _f, _vp]
 _lib.ckl_plan_gemm.argtypes = [_i, _i, _i, _i, _i, _i, _i, _i, _i, _i, ctypes.POINTER(Plan)]
 _lib.ckl_plan_sk_range.argtypes = [ctypes.POINTER(Plan), _i, ctypes.POINTER(ctypes.c_longlong),
                                    ctypes.POINTER(ctypes.c_longlong)]
@@ -77,7 +79,7 @@ _lib.ckl_algo_name.argtypes = [_i]
 _lib.ckl_algo_name.restype = ctypes.c_char_p
 _lib.ckl_shutdown.restype = None
 for _name in ("ckl_gemm_f16", "ckl_gemm_bf16", "ckl_gemm_ex", "ckl_gemm_bias_relu_ex",
-              "ckl_bias_relu_f32", "ckl_gemm_host", "ckl_plan_gemm", "ckl_plan_sk_range",
+              "ckl_bias_relu_f32", "ckl_gemm_host", "ckl_sgemm", "ckl_strsm_lower", "ckl_plan_gemm", "ckl_plan_sk_range",
               "ckl_device_status", "ckl_stream_copy", "ckl_plan_unit_segments",
               "ckl_plan_fixup_slots", "ckl_assemble_column_blocks"):
     getattr(_lib, _name).restype = ctypes.c_int
@@ -145,6 +147,16 @@ gemm_mma_ldm = gemm_wmma_fp16
 gemm_mma_opt = gemm_wmma_fp16
 
 
+def gemm_naive(a, b, c, m, n, k, alpha, beta, stream=None) -> None:
+    """FP32 ladder (include/ckl/gemm.hpp:40-58 of the reference): every rung is ckl_sgemm."""
+    sgemm(a, b, c, m, n, k, k, n, n, alpha, beta, stream)
+
+
+gemm_tiled = gemm_naive
+gemm_register = gemm_naive
+gemm_cp_async = gemm_naive
+
+
 def gemm_mma_opt_bias(a, b, c, bias, m, n, k, alpha, stream=None) -> None:
     """C = relu(alpha*A*B + bias[col]); include/ckl/gemm.hpp:91-92 of the reference."""
     _check(_lib.ckl_gemm_bias_relu_ex(F16, _ptr(a), _ptr(b), _ptr(c), F32, _ptr(bias), m, n, k, k,
@@ -160,6 +172,28 @@ def gemm_bias_relu_ex(ab_dtype, a, b, c, c_dtype, bias, m, n, k, lda, ldb, ldc, 
 def gemm_bias_relu(c, bias, m, n, stream=None) -> None:
     """Unfused pass C = relu(C + bias[col]); include/ckl/gemm.hpp:93 of the reference."""
     _check(_lib.ckl_bias_relu_f32(_ptr(c), _ptr(bias), m, n, n, _stream(stream)))
+
+
+def sgemm(a, b, c, m, n, k, lda=None, ldb=None, ldc=None, alpha=1.0, beta=0.0, stream=None) -> None:
+    """FP32 C = alpha*A*B + beta*C on the CUDA cores (the reference's gemm_naive / gemm_tiled /
+    gemm_register / gemm_cp_async, include/ckl/gemm.hpp:40-58)."""
+    _check(_lib.ckl_sgemm(_ptr(a), _ptr(b), _ptr(c), m, n, k, k if lda is None else lda,
+                          n if ldb is None else ldb, n if ldc is None else ldc, alpha, beta,
+                          _stream(stream)))
+
+
+def strsm_lower(l, b, m, n, lda=None, ldb=None, alpha=1.0, stream=None) -> None:
+    """Solve L X = alpha B in place (L lower triangular m x m, B m x n, FP32, row-major)."""
+    _check(_lib.ckl_strsm_lower(_ptr(l), _ptr(b), m, n, m if lda is None else lda,
+                                n if ldb is None else ldb, alpha, _stream(stream)))
+
+
+def trsm_blocked(a, b, m, n, alpha, stream=None) -> None:
+    """include/ckl/trsm.hpp:19-24 of the reference: both of its rungs are the blocked solve here."""
+    strsm_lower(a, b, m, n, m, n, alpha, stream)
+
+
+trsm_naive = trsm_blocked
 
 
 def gemm_host(ab_dtype, a_host, b_host, c_host, c_dtype, m, n, k, alpha, beta) -> None:

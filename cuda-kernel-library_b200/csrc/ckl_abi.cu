@@ -20,9 +20,11 @@
 #include <cuda_runtime.h>
 
 #include "ckl_gemm.h"
+#include "gemm_fp32.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_umma.cuh"
 #include "tile_sched.h"
+#include "trsm.cuh"
 
 namespace {
 
@@ -636,6 +638,103 @@ int ckl_bias_relu_f32(float* c, const float* bias, int m, int n, int ldc, ckl_st
     const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148LL * 16));
     bias_relu_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(c, bias, m, n, ldc);
     CKL_TRY_CUDA(cudaGetLastError());
+    return CKL_OK;
+}
+
+int ckl_sgemm(const float* a, const float* b, float* c, int m, int n, int k, int lda, int ldb,
+              int ldc, float alpha, float beta, ckl_stream_t stream) {
+    if (m <= 0 || n <= 0) {
+        return CKL_OK;  // nothing to write
+    }
+    if (c == nullptr) {
+        return fail(CKL_ERR_INVALID_ARG, "ckl_sgemm: C is null");
+    }
+    if (ldc < n) {
+        return fail(CKL_ERR_INVALID_ARG, "ckl_sgemm: ldc=%d is smaller than n=%d", ldc, n);
+    }
+    DeviceCtx* ctx = nullptr;
+    if (const int rc = get_ctx(&ctx); rc != CKL_OK) {
+        return rc;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (k <= 0) {
+        return launch_scale<float>(c, nullptr, m, n, ldc, beta, kEpiLinear, s);  // C = beta * C
+    }
+    if (a == nullptr || b == nullptr) {
+        return fail(CKL_ERR_INVALID_ARG, "ckl_sgemm: A or B is null");
+    }
+    if (lda < k || ldb < n) {
+        return fail(CKL_ERR_INVALID_ARG, "ckl_sgemm: lda=%d < k=%d or ldb=%d < n=%d", lda, k, ldb, n);
+    }
+    // 128 x 128 tiles unless they would leave most of the SMs idle (two CTAs fit on an SM).
+    const long long large_tiles = ((static_cast<long long>(m) + 127) / 128) * ((static_cast<long long>(n) + 127) / 128);
+    const int tile = large_tiles >= ctx->sm_count ? fp32::kTileLarge : fp32::kTileSmall;
+    const long long tiles_m = (static_cast<long long>(m) + tile - 1) / tile;
+    const long long tiles_n = (static_cast<long long>(n) + tile - 1) / tile;
+    if (tiles_m > 65535) {
+        return fail(CKL_ERR_TOO_LARGE, "ckl_sgemm: m=%d needs more than 65535 tile rows", m);
+    }
+    const dim3 grid(static_cast<unsigned>(tiles_n), static_cast<unsigned>(tiles_m));
+    const bool vec = reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(b) % 16 == 0 &&
+                     reinterpret_cast<uintptr_t>(c) % 16 == 0 && lda % 4 == 0 && ldb % 4 == 0 &&
+                     ldc % 4 == 0;
+    if (tile == fp32::kTileLarge) {
+        if (vec) {
+            sgemm_kernel<true, 128><<<grid, fp32::kThreads, 0, s>>>(a, b, c, m, n, k, lda, ldb, ldc, alpha, beta);
+        } else {
+            sgemm_kernel<false, 128><<<grid, fp32::kThreads, 0, s>>>(a, b, c, m, n, k, lda, ldb, ldc, alpha, beta);
+        }
+    } else {
+        if (vec) {
+            sgemm_kernel<true, 64><<<grid, fp32::kThreads, 0, s>>>(a, b, c, m, n, k, lda, ldb, ldc, alpha, beta);
+        } else {
+            sgemm_kernel<false, 64><<<grid, fp32::kThreads, 0, s>>>(a, b, c, m, n, k, lda, ldb, ldc, alpha, beta);
+        }
+    }
+    CKL_TRY_CUDA(cudaGetLastError());
+    return CKL_OK;
+}
+
+int ckl_strsm_lower(const float* l, float* b, int m, int n, int lda, int ldb, float alpha,
+                    ckl_stream_t stream) {
+    if (m <= 0 || n <= 0) {
+        return CKL_OK;  // reference: src/trsm/trsm_blocked.cu:65-67
+    }
+    if (l == nullptr || b == nullptr) {
+        return fail(CKL_ERR_INVALID_ARG, "ckl_strsm_lower: L or B is null");
+    }
+    if (lda < m || ldb < n) {
+        return fail(CKL_ERR_INVALID_ARG, "ckl_strsm_lower: lda=%d < m=%d or ldb=%d < n=%d", lda, m, ldb, n);
+    }
+    DeviceCtx* ctx = nullptr;
+    if (const int rc = get_ctx(&ctx); rc != CKL_OK) {
+        return rc;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (alpha != 1.0f) {
+        // L X = alpha B is linear in B: scale once, then solve with alpha = 1
+        if (const int rc = launch_scale<float>(b, nullptr, m, n, ldb, alpha, kEpiLinear, s); rc != CKL_OK) {
+            return rc;
+        }
+    }
+    const unsigned col_blocks = static_cast<unsigned>((n + kTrsmThreads - 1) / kTrsmThreads);
+    for (int k0 = 0; k0 < m; k0 += kTrsmBlock) {
+        const int kb = std::min(kTrsmBlock, m - k0);
+        trsm_diag_block_kernel<<<col_blocks, kTrsmThreads, 0, s>>>(l, b, n, lda, ldb, k0, kb);
+        CKL_TRY_CUDA(cudaGetLastError());
+        const int below = m - (k0 + kb);
+        if (below > 0) {
+            // trailing update, the GEMM step: B[k0+kb:, :] -= L[k0+kb:, k0:k0+kb] * X[k0:k0+kb, :]
+            const float* l_below = l + static_cast<size_t>(k0 + kb) * lda + k0;
+            const float* x_block = b + static_cast<size_t>(k0) * ldb;
+            float* b_below = b + static_cast<size_t>(k0 + kb) * ldb;
+            if (const int rc = ckl_sgemm(l_below, x_block, b_below, below, n, kb, lda, ldb, ldb, -1.0f,
+                                         1.0f, stream);
+                rc != CKL_OK) {
+                return rc;
+            }
+        }
+    }
     return CKL_OK;
 }
 

@@ -14,8 +14,8 @@
 // on `stream`.
 //
 // On this hardware every FP16 "rung" of the reference ladder is the same
-// TMA + tcgen05 kernel; the distinct names survive only for source
-// compatibility.  Additions over the reference are grouped at the end:
+// TMA + tcgen05 kernel and every FP32 rung the same CUDA-core kernel; the
+// distinct names survive only for source compatibility.  Additions over the reference are grouped at the end:
 // 16-bit C, explicit leading dimensions, kernel selection.
 
 #include <stdexcept>
@@ -66,6 +66,22 @@ inline void throw_on_error(int status, const char* who) {
 }
 }  // namespace detail
 
+// ---- reference signatures: FP32 ladder ------------------------------------------
+// The four FP32 rungs (reference lines 40-58) differ only in how the reference stages
+// data; here they are one CUDA-core kernel with true FP32 arithmetic (ckl_sgemm), which
+// is what their 1e-4 agreement with SGEMM requires.
+
+#define CKL_FP32_RUNG(name)                                                                   \
+    inline void name(const float* a, const float* b, float* c, int m, int n, int k, float alpha, \
+                     float beta, cudaStream_t stream = nullptr) {                              \
+        detail::throw_on_error(ckl_sgemm(a, b, c, m, n, k, k, n, n, alpha, beta, stream), #name); \
+    }
+CKL_FP32_RUNG(gemm_naive)
+CKL_FP32_RUNG(gemm_tiled)
+CKL_FP32_RUNG(gemm_register)
+CKL_FP32_RUNG(gemm_cp_async)
+#undef CKL_FP32_RUNG
+
 // ---- reference signatures: FP16 / BF16 in, FP32 C out ---------------------------
 
 inline void gemm_wmma_fp16(const __half* a, const __half* b, float* c, int m, int n, int k,
@@ -115,9 +131,11 @@ inline void gemm_bias_relu(float* c, const float* bias, int m, int n,
     detail::throw_on_error(ckl_bias_relu_f32(c, bias, m, n, n, stream), "gemm_bias_relu");
 }
 
-// cuBLAS comparators (cublasGemmEx, FP32 C).  Test and benchmark code only:
-// they are defined in a separate translation unit that the shipped library
-// does not contain (reference: src/gemm/cublas_gemm_ex.cpp:56-66).
+// cuBLAS comparators (SGEMM; cublasGemmEx with FP32 C).  Test and benchmark code
+// only: they are defined in separate translation units that the shipped library
+// does not contain (reference: src/gemm/cublas_gemm.cpp, src/gemm/cublas_gemm_ex.cpp:56-66).
+void gemm_cublas(const float* a, const float* b, float* c, int m, int n, int k, float alpha,
+                 float beta, cudaStream_t stream = nullptr);
 void gemm_cublas_fp16(const __half* a, const __half* b, float* c, int m, int n, int k, float alpha,
                       float beta, cudaStream_t stream = nullptr);
 void gemm_cublas_bf16(const __nv_bfloat16* a, const __nv_bfloat16* b, float* c, int m, int n, int k,

@@ -92,6 +92,30 @@ int ckl_gemm_bias_relu_ex(int ab_dtype, const void* a, const void* b, void* c, i
                           float alpha, int algo, ckl_stream_t stream);
 int ckl_bias_relu_f32(float* c, const float* bias, int m, int n, int ldc, ckl_stream_t stream);
 
+/* Single-precision GEMM, C = alpha*A*B + beta*C with FP32 inputs, FP32 multiply-add
+ * and FP32 C (no tensor cores: the reference's FP32 tests demand agreement with
+ * SGEMM to 1e-4, tests/test_gemm.cpp:50,98-101).  Replaces the reference's four
+ * FP32 rungs ckl::gemm_naive / gemm_tiled / gemm_register / gemm_cp_async
+ * (include/ckl/gemm.hpp:40-58; src/gemm/gemm_naive.cu, gemm_tiled.cu,
+ * gemm_register.cu, gemm_cp_async.cu), which all compute this with the same
+ * signature.  Row-major, explicit leading dimensions, any shape and alignment;
+ * m <= 0 or n <= 0 is a no-op, k <= 0 scales C by beta; C is not read when
+ * beta == 0.  Stream-ordered, allocates nothing. */
+int ckl_sgemm(const float* a, const float* b, float* c, int m, int n, int k, int lda, int ldb,
+              int ldc, float alpha, float beta, ckl_stream_t stream);
+
+/* Triangular solve with many right-hand sides, L X = alpha B: L is m x m lower
+ * triangular with a non-unit diagonal (its upper part is not read), B is m x n
+ * and is overwritten by X; FP32, row-major, explicit leading dimensions.
+ * Blocked: 64-row diagonal blocks are solved directly, everything below a block
+ * is updated with one ckl_sgemm call, so the bulk of the flops run in the GEMM.
+ * Replaces ckl::trsm_naive and ckl::trsm_blocked (include/ckl/trsm.hpp:19-24;
+ * src/trsm/trsm_naive.cu, src/trsm/trsm_blocked.cu:64-92), whose blocked form
+ * updates the trailing rows with a one-thread-per-element loop instead of a
+ * GEMM.  m <= 0 or n <= 0 is a no-op.  Stream-ordered, allocates nothing. */
+int ckl_strsm_lower(const float* l, float* b, int m, int n, int lda, int ldb, float alpha,
+                    ckl_stream_t stream);
+
 /* Whole call with HOST buffers: copies A, B (and C when beta != 0) to device
  * memory the library keeps per device, runs the GEMM, copies C back and waits.
  * This is what a caller holding host matrices pays end to end; it is the

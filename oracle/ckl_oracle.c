@@ -14,6 +14,8 @@
  *   - the host float -> FP16 / BF16 narrowing the reference tests apply to
  *     the random floats before upload (tests/test_gemm_tensor.cpp:40-56,
  *     round to nearest even)
+ *   - the helpers of the reference's triangular-solve test: make_lower,
+ *     trsm_reference and residual (tests/test_trsm.cpp:20-69)
  *
  * random_matrix in the reference is std::mt19937_64 driving
  * std::uniform_real_distribution<float>(-1, 1) as implemented by libstdc++
@@ -310,4 +312,56 @@ int ckl_oracle_max_threads(void) {
 #else
     return 1;
 #endif
+}
+
+/* ------------------------------------------------------------------------ */
+/* Triangular solve helpers of the reference's TRSM test                     */
+/* ------------------------------------------------------------------------ */
+
+/* tests/test_trsm.cpp:20-31 of the reference: random_matrix(m, m, seed) with the upper
+ * part zeroed and the diagonal set to m + 1 (diagonally dominant, well conditioned). */
+void ckl_oracle_make_lower(int m, uint64_t seed, float* out) {
+    ckl_oracle_random_matrix(m, m, seed, out);
+    for (int i = 0; i < m; ++i) {
+        for (int j = i + 1; j < m; ++j) {
+            out[(size_t)i * m + j] = 0.0f;
+        }
+        out[(size_t)i * m + i] = (float)(m + 1);
+    }
+}
+
+/* tests/test_trsm.cpp:33-47: forward substitution in double, column by column,
+ * x[i] = (alpha * b[i] - sum_{j<i} a[i][j] * x[j]) / a[i][i], the sum taken in order of j. */
+void ckl_oracle_trsm_reference(const float* a, const float* b, int m, int n, float alpha, double* x) {
+#ifdef _OPENMP
+#pragma omp parallel for schedule(static)
+#endif
+    for (int c = 0; c < n; ++c) {
+        for (int i = 0; i < m; ++i) {
+            double s = (double)alpha * b[(size_t)i * n + c];
+            for (int j = 0; j < i; ++j) {
+                s -= (double)a[(size_t)i * m + j] * x[(size_t)j * n + c];
+            }
+            x[(size_t)i * n + c] = s / a[(size_t)i * m + i];
+        }
+    }
+}
+
+/* tests/test_trsm.cpp:50-69: ||L X - alpha B||_F / ||alpha B||_F in double. */
+double ckl_oracle_trsm_residual(const float* a, const float* x, const float* b, int m, int n,
+                                float alpha) {
+    double num = 0.0;
+    double den = 0.0;
+    for (int i = 0; i < m; ++i) {
+        for (int c = 0; c < n; ++c) {
+            double lx = 0.0;
+            for (int j = 0; j <= i; ++j) {
+                lx += (double)a[(size_t)i * m + j] * (double)x[(size_t)j * n + c];
+            }
+            const double target = (double)alpha * (double)b[(size_t)i * n + c];
+            num += (lx - target) * (lx - target);
+            den += target * target;
+        }
+    }
+    return sqrt(num) / sqrt(den);
 }

@@ -24,6 +24,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "libckl_oracle.so")
 _REF_PATH = os.path.join(_HERE, "_ref", "libckl_ref.so")
+_REF_TRSM_PATH = os.path.join(_HERE, "_ref", "libckl_ref_trsm.so")
 
 F16 = 1
 BF16 = 2
@@ -189,6 +190,56 @@ class Reference(_Lib):
 
     def __init__(self):
         super().__init__(_REF_PATH, "ckl_ref_")
+
+
+class TrsmHelpers:
+    """make_lower / trsm_reference / residual of the reference's TRSM test
+    (tests/test_trsm.cpp:20-69): the plain-C port by default, or the reference's own code
+    from oracle/_ref/libckl_ref_trsm.so with ``from_reference=True``."""
+
+    def __init__(self, from_reference: bool = False):
+        if from_reference:
+            self.lib, prefix = ctypes.CDLL(_REF_TRSM_PATH), "ckl_ref_"
+        else:
+            if not os.path.exists(_LIB_PATH):
+                build()
+            self.lib, prefix = ctypes.CDLL(_LIB_PATH), "ckl_oracle_"
+        self._make_lower = getattr(self.lib, prefix + "make_lower")
+        self._make_lower.argtypes = [ctypes.c_int, ctypes.c_uint64, _fp]
+        self._make_lower.restype = None
+        self._solve = getattr(self.lib, prefix + "trsm_reference")
+        self._solve.argtypes = [_fp, _fp, ctypes.c_int, ctypes.c_int, ctypes.c_float, _dp]
+        self._solve.restype = None
+        self._residual = getattr(self.lib, prefix + "trsm_residual")
+        self._residual.argtypes = [_fp, _fp, _fp, ctypes.c_int, ctypes.c_int, ctypes.c_float]
+        self._residual.restype = ctypes.c_double
+
+    def make_lower(self, m: int, seed: int) -> np.ndarray:
+        out = np.empty((m, m), dtype=np.float32)
+        if out.size:
+            self._make_lower(m, seed, _f(out))
+        return out
+
+    def trsm_reference(self, a, b, alpha: float) -> np.ndarray:
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        b = np.ascontiguousarray(b, dtype=np.float32)
+        m, n = b.shape
+        assert a.shape == (m, m)
+        x = np.empty((m, n), dtype=np.float64)
+        if x.size:
+            self._solve(_f(a), _f(b), m, n, alpha, _d(x))
+        return x
+
+    def trsm_residual(self, a, x, b, alpha: float) -> float:
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        b = np.ascontiguousarray(b, dtype=np.float32)
+        m, n = b.shape
+        return float(self._residual(_f(a), _f(x), _f(b), m, n, alpha))
+
+
+def have_reference_trsm() -> bool:
+    return os.path.exists(_REF_TRSM_PATH)
 
 
 class RowBlockTimer:

@@ -75,5 +75,32 @@ def main() -> None:
     print("wrote", path)
 
 
+def trsm_main() -> None:
+    """tests/golden/trsm_kat.json from the helpers of the reference's TRSM test
+    (oracle/_ref/libckl_ref_trsm.so = tests/test_trsm.cpp of the reference, compiled where it
+    lies); shapes, seeds and alpha are that test's (lines 92-95, 122-126)."""
+    gemm_ref = oracle.Reference()
+    ref = oracle.TrsmHelpers(from_reference=True)
+    out = {"generator": "oracle/_ref/libckl_ref_trsm.so (reference tests/test_trsm.cpp, g++ -O2)",
+           "cases": []}
+    for m, n in [(256, 128), (512, 64), (129, 200), (5, 3), (64, 1), (65, 130)]:
+        alpha = 1.5
+        a = ref.make_lower(m, 0x71 + m)
+        b = gemm_ref.random_matrix(m, n, 0x92 + n)
+        x = ref.trsm_reference(a, b, alpha)
+        entry = {"m": m, "n": n, "alpha": alpha, "lower_sha256": sha(a), "x_sha256": sha(x),
+                 "x_first": float(x.ravel()[0]), "x_last": float(x.ravel()[-1]), "x_sum": float(x.sum()),
+                 "residual_of_rounded_x": ref.trsm_residual(a, x.astype(np.float32), b, alpha)}
+        if m * n <= 64:
+            entry["x_full"] = [float(v) for v in x.ravel()]
+        out["cases"].append(entry)
+    path = os.path.join(ROOT, "tests", "golden", "trsm_kat.json")
+    with open(path, "w") as f:
+        json.dump(out, f, indent=1)
+    print("wrote", path)
+
+
 if __name__ == "__main__":
-    main()
+    if "--trsm-only" not in sys.argv:
+        main()
+    trsm_main()

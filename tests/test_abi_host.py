@@ -37,6 +37,22 @@ def test_reference_entry_points_are_mirrored(ckl):
         assert re.search(rf"\b{name}\s*\(", header), name
 
 
+def test_fp32_ladder_is_mirrored_and_validates(ckl):
+    # include/ckl/gemm.hpp:40-58 of the reference: the four FP32 rungs.
+    header = open(os.path.join(ROOT, "include", "ckl", "gemm.hpp")).read()
+    for name in ("gemm_naive", "gemm_tiled", "gemm_register", "gemm_cp_async"):
+        assert callable(getattr(ckl, name))
+        assert re.search(rf"CKL_FP32_RUNG\({name}\)", header), name
+    ckl.gemm_naive(None, None, None, 0, 128, 128, 1.25, 0.5)   # zero m: no-op, as the reference
+    ckl.gemm_cp_async(None, None, None, 128, 0, 128, 1.25, 0.5)
+    with pytest.raises(ckl.CklError) as e:
+        ckl.sgemm(16, 16, None, 4, 4, 4)                       # C null
+    assert e.value.status == ckl.ERR_INVALID_ARG
+    with pytest.raises(ckl.CklError) as e:
+        ckl.sgemm(16, 16, 16, 4, 8, 4, 4, 8, 4)                # ldc < n
+    assert e.value.status == ckl.ERR_INVALID_ARG
+
+
 def test_argument_validation_needs_no_gpu(ckl):
     # bad dtypes / algo / leading dimension are rejected before any CUDA call
     with pytest.raises(ckl.CklError) as e:

@@ -430,3 +430,14 @@ def test_reference_test_driver_runs_unchanged(env):
     print(out.stdout[-4000:])
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
     assert "all tensor GEMM cases passed" in out.stdout
+
+
+def test_reference_fusion_study_runs_unchanged(env):
+    """The reference's benchmarks/fusion_study.cpp (fused bias+ReLU epilogue against GEMM plus a
+    separate pass), compiled without edits against this repository's headers and library."""
+    exe = os.path.join(ROOT, "oracle", "_ref", "fusion_study_dropin")
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref/fusion_study_dropin not built (needs the reference tree)")
+    out = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    print(out.stdout[-4000:])
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
