@@ -13,6 +13,7 @@
 #include <memory>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -718,22 +719,39 @@ int ckl_strsm_lower(const float* l, float* b, int m, int n, int lda, int ldb, fl
         }
     }
     const unsigned col_blocks = static_cast<unsigned>((n + kTrsmThreads - 1) / kTrsmThreads);
-    for (int k0 = 0; k0 < m; k0 += kTrsmBlock) {
-        const int kb = std::min(kTrsmBlock, m - k0);
-        trsm_diag_block_kernel<<<col_blocks, kTrsmThreads, 0, s>>>(l, b, n, lda, ldb, k0, kb);
-        CKL_TRY_CUDA(cudaGetLastError());
-        const int below = m - (k0 + kb);
-        if (below > 0) {
-            // trailing update, the GEMM step: B[k0+kb:, :] -= L[k0+kb:, k0:k0+kb] * X[k0:k0+kb, :]
-            const float* l_below = l + static_cast<size_t>(k0 + kb) * lda + k0;
-            const float* x_block = b + static_cast<size_t>(k0) * ldb;
-            float* b_below = b + static_cast<size_t>(k0 + kb) * ldb;
-            if (const int rc = ckl_sgemm(l_below, x_block, b_below, below, n, kb, lda, ldb, ldb, -1.0f,
-                                         1.0f, stream);
-                rc != CKL_OK) {
-                return rc;
-            }
+    // Recursive halving, written as an explicit stack of (first row, rows, stage) so that no
+    // recursion depth depends on m.  stage 0: split or solve; stage 1: the upper half is solved,
+    // update the lower half with one GEMM and descend into it.
+    struct Frame {
+        int r0, rows, stage;
+    };
+    std::vector<Frame> stack;
+    stack.push_back({0, m, 0});
+    while (!stack.empty()) {
+        const Frame f = stack.back();
+        stack.pop_back();
+        if (f.rows <= kTrsmBlock) {
+            trsm_diag_block_kernel<<<col_blocks, kTrsmThreads, 0, s>>>(l, b, n, lda, ldb, f.r0, f.rows);
+            CKL_TRY_CUDA(cudaGetLastError());
+            continue;
         }
+        // upper half: a multiple of the block size, so diagonal blocks stay aligned
+        const int up = ((f.rows / 2 + kTrsmBlock - 1) / kTrsmBlock) * kTrsmBlock;
+        if (f.stage == 0) {
+            stack.push_back({f.r0, f.rows, 1});
+            stack.push_back({f.r0, up, 0});
+            continue;
+        }
+        // B[r0+up : r0+rows, :] -= L[r0+up : r0+rows, r0 : r0+up] * X[r0 : r0+up, :]
+        const float* l_low = l + static_cast<size_t>(f.r0 + up) * lda + f.r0;
+        const float* x_up = b + static_cast<size_t>(f.r0) * ldb;
+        float* b_low = b + static_cast<size_t>(f.r0 + up) * ldb;
+        if (const int rc = ckl_sgemm(l_low, x_up, b_low, f.rows - up, n, up, lda, ldb, ldb, -1.0f, 1.0f,
+                                     stream);
+            rc != CKL_OK) {
+            return rc;
+        }
+        stack.push_back({f.r0 + up, f.rows - up, 0});
     }
     return CKL_OK;
 }

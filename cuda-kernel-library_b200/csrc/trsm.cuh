@@ -1,9 +1,10 @@
 // Diagonal-block kernel of the blocked triangular solve L X = alpha B (L lower triangular,
-// non-unit diagonal, row-major; X overwrites B).  The solve walks down the diagonal in blocks
-// of kTrsmBlock rows: this kernel solves one block row against the block's own triangle, and
-// everything below it is updated by one FP32 GEMM (B_below -= L_below,block * X_block), which is
-// where the flops are.  The reference does the same split but with a one-thread-per-element
-// update loop in place of a GEMM (src/trsm/trsm_blocked.cu:46-62,77-90 there).
+// non-unit diagonal, row-major; X overwrites B).  The solve splits the rows in two halves
+// recursively: solve the upper half, subtract its contribution from the lower half with one FP32
+// GEMM (B_low -= L_low,up * X_up), solve the lower half.  Halves of at most kTrsmBlock rows are
+// solved by this kernel against their own triangle; the GEMMs are where the flops are.  The
+// reference walks down the diagonal in 32-row blocks and updates the rows below each with a
+// one-thread-per-element loop in place of a GEMM (src/trsm/trsm_blocked.cu:46-62,77-90 there).
 #pragma once
 
 #include <cstddef>
@@ -36,25 +37,33 @@ trsm_diag_block_kernel(const float* __restrict__ l, float* b, int n, int lda, in
     if (col >= n) {
         return;
     }
+    // All right-hand-side values of the block are fetched before the first row is solved and
+    // written back after the last: loads and stores go through the same pointer, so interleaved
+    // they would have to stay in program order and every row would wait a global-memory round trip.
     float x[kTrsmBlock];
     float* bcol = b + static_cast<size_t>(k0) * ldb + col;
 #pragma unroll
     for (int i = 0; i < kTrsmBlock; ++i) {
-        if (i < kb) {
-            float s0 = bcol[static_cast<size_t>(i) * ldb];
-            float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+        x[i] = i < kb ? bcol[static_cast<size_t>(i) * ldb] : 0.0f;
+    }
 #pragma unroll
-            for (int j = 0; j < i; ++j) {
-                const float t = tri[i][j] * x[j];
-                if ((j & 3) == 0) s0 -= t;
-                if ((j & 3) == 1) s1 -= t;
-                if ((j & 3) == 2) s2 -= t;
-                if ((j & 3) == 3) s3 -= t;
-            }
-            x[i] = ((s0 + s1) + (s2 + s3)) / tri[i][i];
+    for (int i = 0; i < kTrsmBlock; ++i) {
+        float s0 = x[i], s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+#pragma unroll
+        for (int j = 0; j < i; ++j) {
+            const float t = tri[i][j] * x[j];
+            if ((j & 3) == 0) s0 -= t;
+            if ((j & 3) == 1) s1 -= t;
+            if ((j & 3) == 2) s2 -= t;
+            if ((j & 3) == 3) s3 -= t;
+        }
+        // rows past kb have a zero triangle row and a zero right-hand side; keep them at zero
+        x[i] = i < kb ? ((s0 + s1) + (s2 + s3)) / tri[i][i] : 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < kTrsmBlock; ++i) {
+        if (i < kb) {
             bcol[static_cast<size_t>(i) * ldb] = x[i];
-        } else {
-            x[i] = 0.0f;
         }
     }
 }

@@ -37,6 +37,10 @@ FIELDS = ["family", "variant", "dtype", "m", "n", "k", "gpus", "median_ms", "iqr
           "max_temp_c", "max_power_w", "throttled", "power_capped", "commit"]
 
 
+FP32_SIZES = [512, 1024, 2048, 4096]                        # benchmarks/sweep.py:38 there
+TRSM_SIZES = [512, 1024, 2048]                              # benchmarks/sweep.py:42,66-68 there
+
+
 def matrix(quick: bool):
     sizes = [(s, s, s) for s in (SQUARE[:3] if quick else SQUARE)]
     shapes = sizes + ([] if quick else SHAPES)
@@ -45,6 +49,11 @@ def matrix(quick: bool):
             for m, n, k in shapes:
                 yield {"family": "gemm", "variant": variant, "dtype": dtype, "m": m, "n": n, "k": k,
                        "gpus": 1}
+    for s in (FP32_SIZES[1:3] if quick else FP32_SIZES):
+        yield {"family": "gemm", "variant": "sgemm", "dtype": "fp32", "m": s, "n": s, "k": s, "gpus": 1}
+    for s in (TRSM_SIZES[1:2] if quick else TRSM_SIZES):
+        yield {"family": "trsm", "variant": "blocked", "dtype": "fp32", "m": s, "n": 256, "k": 0,
+               "gpus": 1}
 
 
 def key_of(row: dict) -> tuple:
@@ -80,7 +89,7 @@ def current_commit() -> str:
 
 def run_one(cfg: dict, commit: str, runner=None) -> dict | None:
     """Runs one configuration in its own process; returns the parsed row or None."""
-    cmd = [BENCH_ALL, "gemm", cfg["variant"], cfg["dtype"], str(cfg["m"]), str(cfg["n"]),
+    cmd = [BENCH_ALL, cfg["family"], cfg["variant"], cfg["dtype"], str(cfg["m"]), str(cfg["n"]),
            str(cfg["k"]), commit]
     env = dict(os.environ, CKL_REPO_ROOT=ROOT)
     proc = (runner or subprocess.run)(cmd, capture_output=True, text=True, env=env, timeout=600)

@@ -152,4 +152,16 @@ inline CublasFn16 find_cublas_comparator(const std::string& repo_root, bool bf16
     return reinterpret_cast<CublasFn16>(dlsym(lib, name));
 }
 
+// The reference's SGEMM wrapper (ckl::gemm_cublas, src/gemm/cublas_gemm.cpp), same lookup.
+using CublasFn32 = void (*)(const float*, const float*, float*, int, int, int, float, float,
+                            cudaStream_t);
+inline CublasFn32 find_sgemm_comparator(const std::string& repo_root) {
+    const std::string path = repo_root + "/oracle/_ref/libckl_ref_gemm.so";
+    void* lib = dlopen(path.c_str(), RTLD_NOW | RTLD_LOCAL);
+    if (lib == nullptr) {
+        return nullptr;
+    }
+    return reinterpret_cast<CublasFn32>(dlsym(lib, "_ZN3ckl11gemm_cublasEPKfS1_PfiiiffP11CUstream_st"));
+}
+
 }  // namespace ckl_tools

@@ -10,9 +10,11 @@
 // Writes <out_dir>/roofline_ceilings.csv and <out_dir>/roofline.csv in the
 // column layout the reference's plotting script reads.
 
+#include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "ckl/device_buffer.hpp"
@@ -65,6 +67,10 @@ int main(int argc, char** argv) {
         db.copy_from_host(hb);
         dc.zero();
         for (int algo : {CKL_ALGO_AUTO, CKL_ALGO_UMMA_1CTA, CKL_ALGO_UMMA_2CTA, CKL_ALGO_UMMA_2CTA_WIDE}) {
+            // each variant starts from an idle GPU: back to back, the later ones would be
+            // measured at the lower clock the power limit imposes after ~50 launches
+            cudaDeviceSynchronize();
+            std::this_thread::sleep_for(std::chrono::milliseconds(700));
             const ckl::TimingStats t = ckl::time_stream([&](cudaStream_t s) {
                 ckl_gemm_ex(CKL_BF16, da.data(), db.data(), dc.data(), CKL_BF16, size, size, size, size,
                             size, size, 1.0f, 0.0f, algo, s);
@@ -87,6 +93,37 @@ int main(int argc, char** argv) {
             }
         }
     }
+    // FP32 (CUDA-core) rung and roof: ckl_sgemm at 4096^3; the roof is SGEMM through the
+    // reference's cuBLAS wrapper when that build is present, as in the reference's profiler
+    // (src/profiler/roofline.cpp:40-53), else 2 FLOP x 128 lanes x SMs x boost clock.
+    double fp32_peak = prop.multiProcessorCount * 256.0 * core_khz * 1.0e3;
+    bool fp32_measured = false;
+    {
+        const int size = 4096;
+        const auto ha = ckl::random_matrix(size, size, 3);
+        const auto hb = ckl::random_matrix(size, size, 4);
+        ckl::DeviceBuffer<float> da(ha.size()), db(hb.size()), dc(ha.size());
+        da.copy_from_host(ha);
+        db.copy_from_host(hb);
+        dc.zero();
+        const ckl::TimingStats t = ckl::time_stream([&](cudaStream_t s) {
+            ckl_sgemm(da.data(), db.data(), dc.data(), size, size, size, size, size, size, 1.0f, 0.0f, s);
+        });
+        ckl::RooflinePoint pt;
+        pt.label = "gemm_cp_async";  // the top FP32 rung's name in the reference's figure
+        pt.flops = ckl::gemm_flops(size, size, size);
+        pt.bytes = ckl::gemm_bytes(size, size, size, sizeof(float));
+        pt.achieved_flops_per_s = pt.flops / (t.median_ms * 1.0e-3);
+        pt.tensor = false;
+        points.push_back(pt);
+        if (auto sgemm = ckl_tools::find_sgemm_comparator(root)) {
+            const ckl::TimingStats tc = ckl::time_stream([&](cudaStream_t s) {
+                sgemm(da.data(), db.data(), dc.data(), size, size, size, 1.0f, 0.0f, s);
+            });
+            fp32_peak = ckl::gemm_flops(size, size, size) / (tc.median_ms * 1.0e-3);
+            fp32_measured = true;
+        }
+    }
     if (ckl_device_status(nullptr) != CKL_OK) {
         std::fprintf(stderr, "ckl error: %s\n", ckl_last_error());
         return 1;
@@ -103,12 +140,15 @@ int main(int argc, char** argv) {
                 cublas_peak > 0.0 ? "cuBLAS BF16 8192^3, the reference's definition" : "datasheet");
     std::printf("  datasheet dense 16-bit        : %.1f TFLOP/s\n", datasheet / 1.0e12);
     std::printf("  SMs x 8192 x boost clock      : %.1f TFLOP/s\n", clock_derived / 1.0e12);
+    std::printf("  FP32 roof                     : %.1f TFLOP/s (%s)\n", fp32_peak / 1.0e12,
+                fp32_measured ? "cuBLAS SGEMM 4096^3, the reference's definition" : "lanes x clock");
     std::printf("  ridge                         : %.1f FLOP/byte\n", ridge);
 
     const std::string ceilings = out_dir + "/roofline_ceilings.csv";
     if (std::FILE* f = std::fopen(ceilings.c_str(), "w")) {
-        std::fprintf(f, "quantity,value\nbandwidth_gbps,%.3f\ntensor_gflops,%.3f\n", bw / 1.0e9,
-                     tensor_peak / 1.0e9);
+        std::fprintf(f, "quantity,value\nbandwidth_gbps,%.3f\nfp32_gflops,%.3f\ntensor_gflops,%.3f\n",
+                     bw / 1.0e9, fp32_peak / 1.0e9, tensor_peak / 1.0e9);
+        std::fprintf(f, "ridge_fp32,%.3f\n", ckl::ridge_intensity(fp32_peak, bw));
         std::fprintf(f, "tensor_gflops_datasheet,%.3f\ntensor_gflops_clock_derived,%.3f\nridge_tensor,%.3f\n",
                      datasheet / 1.0e9, clock_derived / 1.0e9, ridge);
         std::fclose(f);
@@ -121,13 +161,14 @@ int main(int argc, char** argv) {
     std::printf("%-36s %10s %12s %12s %9s %s\n", "variant", "intensity", "gflops", "roof_gflops",
                 "pct_roof", "bound");
     for (const auto& p : points) {
-        const double roof = ckl::roofline_flops(p.intensity(), tensor_peak, bw) / 1.0e9;
-        const char* bound = p.intensity() < ridge ? "memory" : "compute";
+        const double peak = p.tensor ? tensor_peak : fp32_peak;
+        const double roof = ckl::roofline_flops(p.intensity(), peak, bw) / 1.0e9;
+        const char* bound = p.intensity() < ckl::ridge_intensity(peak, bw) ? "memory" : "compute";
         std::printf("%-36s %10.1f %12.1f %12.1f %8.1f%% %s\n", p.label.c_str(), p.intensity(),
                     p.achieved_gflops(), roof, 100.0 * p.achieved_gflops() / roof, bound);
         if (csv != nullptr) {
-            std::fprintf(csv, "%s,%.4f,%.1f,%.1f,tensor,%s\n", p.label.c_str(), p.intensity(),
-                         p.achieved_gflops(), roof, bound);
+            std::fprintf(csv, "%s,%.4f,%.1f,%.1f,%s,%s\n", p.label.c_str(), p.intensity(),
+                         p.achieved_gflops(), roof, p.tensor ? "tensor" : "fp32", bound);
         }
     }
     if (csv != nullptr) {

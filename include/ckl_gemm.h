@@ -107,8 +107,9 @@ int ckl_sgemm(const float* a, const float* b, float* c, int m, int n, int k, int
 /* Triangular solve with many right-hand sides, L X = alpha B: L is m x m lower
  * triangular with a non-unit diagonal (its upper part is not read), B is m x n
  * and is overwritten by X; FP32, row-major, explicit leading dimensions.
- * Blocked: 64-row diagonal blocks are solved directly, everything below a block
- * is updated with one ckl_sgemm call, so the bulk of the flops run in the GEMM.
+ * Recursive halving: solve the upper half of the rows, subtract its contribution
+ * from the lower half with one ckl_sgemm call, solve the lower half; halves of at
+ * most 64 rows are solved directly.  The bulk of the flops run in the GEMMs.
  * Replaces ckl::trsm_naive and ckl::trsm_blocked (include/ckl/trsm.hpp:19-24;
  * src/trsm/trsm_naive.cu, src/trsm/trsm_blocked.cu:64-92), whose blocked form
  * updates the trailing rows with a one-thread-per-element loop instead of a

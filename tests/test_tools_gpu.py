@@ -46,6 +46,30 @@ def test_bench_all_row():
     assert bad.returncode == 3
 
 
+def test_bench_all_fp32_and_trsm_rows():
+    row = json.loads(_run(["bench_all", "gemm", "sgemm", "fp32", "1024", "1024", "1024", "t"]).strip())
+    assert row["family"] == "gemm" and row["dtype"] == "fp32" and row["gflops"] > 1000
+    row = json.loads(_run(["bench_all", "trsm", "blocked", "fp32", "1024", "512", "0", "t"]).strip())
+    assert row["family"] == "trsm" and row["variant"] == "blocked" and row["gflops"] > 100
+
+
+def test_roofline_writes_the_figure_inputs(tmp_path):
+    """The two CSV files the reference's scripts/plot_roofline.py reads (its lines 53-61, 84-91,
+    139-141): ceilings by quantity, points with label / intensity / achieved / ceiling."""
+    import csv
+    _run(["roofline", str(tmp_path)])
+    with open(tmp_path / "roofline_ceilings.csv") as f:
+        ceilings = {r["quantity"]: float(r["value"]) for r in csv.DictReader(f)}
+    for key in ("bandwidth_gbps", "fp32_gflops", "tensor_gflops", "ridge_fp32", "ridge_tensor"):
+        assert ceilings[key] > 0, key
+    assert ceilings["tensor_gflops"] > 10 * ceilings["fp32_gflops"]
+    with open(tmp_path / "roofline.csv") as f:
+        points = list(csv.DictReader(f))
+    assert {"label", "intensity_flop_per_byte", "achieved_gflops", "roof_gflops", "ceiling",
+            "bound"} <= set(points[0])
+    assert {p["ceiling"] for p in points} == {"tensor", "fp32"}
+
+
 def test_stream_copy_is_exact(ckl):
     import torch
     for nbytes in (1 << 26, 1_000_016, 16):
