@@ -63,6 +63,7 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 struct Staging {
     void* ptr = nullptr;
     size_t bytes = 0;
+    unsigned int epoch = 0;  // stream-K workspaces: value of the "partial is ready" flags of the last launch
 };
 
 struct DeviceCtx {
@@ -236,10 +237,16 @@ Schedule make_schedule(int m, int n, int k, int mode, int max_units, int want_sk
     }
     const long long sk_iters = static_cast<long long>(sk_tiles) * s.k_blocks;
     if (want_sk == 2) {
-        // Heuristic (measured): the split pays for its partial-tile traffic and fix-up
-        // pass when whole tiles would leave a quarter or more of the machine idle and
-        // every unit still gets a long run of k blocks.
-        if (full_waves >= 1 || tiles * 4 > max_units * 3 || sk_iters / max_units < 8) {
+        // Heuristic (measured).  Fewer tiles than units: the split pays for its partial-tile
+        // traffic and fix-up pass when whole tiles would leave a quarter or more of the
+        // machine idle and every unit still gets a long run of k blocks.  One or more full
+        // waves: the split (fused, hidden behind the whole tiles) pays when the last wave
+        // would be at most 60 % full (4096^3: 34 of 74; at 78 % and above it measured a loss).
+        if (full_waves >= 1) {
+            if (rem * 10 > max_units * 6) {
+                return s;
+            }
+        } else if (tiles * 4 > max_units * 3 || sk_iters / max_units < 8) {
             return s;
         }
     }
@@ -309,6 +316,9 @@ int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_al
     int want_sk = 0;
     if (is_sk_algo(resolved)) {
         want_sk = (algo == CKL_ALGO_AUTO) ? 2 : 1;
+        if (algo == CKL_ALGO_AUTO && mode == kModePairWide) {
+            want_sk = 0;  // one accumulator: a split tile's reduction cannot hide behind the next tile
+        }
     }
     const int max_units = pair ? max_pairs : sm_count;
     if (max_units <= 0) {
@@ -361,20 +371,40 @@ int encode_2d(DeviceCtx* ctx, CUtensorMap* map, int dtype, const void* base, uin
     return CKL_OK;
 }
 
-int get_workspace(DeviceCtx* ctx, cudaStream_t stream, size_t bytes, float** out) {
+// Stream-K workspace of a stream: [flag words][partial-tile slots].  The flags (one word per
+// slot, 32-row group and accumulator half) are zeroed when the buffer is created; every launch
+// that uses them gets a fresh non-zero epoch, so they never need clearing between launches.
+constexpr size_t kFlagWordsPerSlot = 16;
+size_t flag_region_bytes(const DeviceCtx* ctx) {
+    const size_t bytes = 2ull * static_cast<size_t>(ctx->sm_count) * kFlagWordsPerSlot * sizeof(unsigned int);
+    return (bytes + 255) / 256 * 256;
+}
+
+int get_workspace(DeviceCtx* ctx, cudaStream_t stream, size_t bytes, float** slots,
+                  unsigned int** flags, unsigned int* epoch) {
     std::lock_guard<std::mutex> lock(ctx->mu);
     Staging& w = ctx->workspace[stream];
-    if (w.bytes < bytes) {
+    const size_t flag_bytes = flag_region_bytes(ctx);
+    const size_t total = flag_bytes + bytes;
+    if (w.bytes < total) {
         if (w.ptr != nullptr) {
             CKL_TRY_CUDA(cudaStreamSynchronize(stream));
             CKL_TRY_CUDA(cudaFree(w.ptr));
             w.ptr = nullptr;
             w.bytes = 0;
         }
-        CKL_TRY_CUDA(cudaMalloc(&w.ptr, bytes));
-        w.bytes = bytes;
+        CKL_TRY_CUDA(cudaMalloc(&w.ptr, total));
+        w.bytes = total;
+        w.epoch = 0;
+        CKL_TRY_CUDA(cudaMemsetAsync(w.ptr, 0, flag_bytes, stream));
     }
-    *out = static_cast<float*>(w.ptr);
+    if (++w.epoch == 0) {
+        w.epoch = 1;  // wrapped: zero is the "never written" value (a stale equal epoch would
+                      // need 2^32 launches on one stream between two uses of the same slot)
+    }
+    *flags = static_cast<unsigned int*>(w.ptr);
+    *slots = reinterpret_cast<float*>(static_cast<unsigned char*>(w.ptr) + flag_bytes);
+    *epoch = w.epoch;
     return CKL_OK;
 }
 
@@ -389,20 +419,37 @@ int launch_umma(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
     cfg.blockDim = dim3(Cfg::kThreads);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr;
+    cudaLaunchAttribute attrs[2];
+    unsigned num_attrs = 0;
     if (Cfg::kPair) {
-        attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = 2;
-        attr.val.clusterDim.y = 1;
-        attr.val.clusterDim.z = 1;
-        cfg.attrs = &attr;
-        cfg.numAttrs = 1;
+        attrs[num_attrs].id = cudaLaunchAttributeClusterDimension;
+        attrs[num_attrs].val.clusterDim.x = 2;
+        attrs[num_attrs].val.clusterDim.y = 1;
+        attrs[num_attrs].val.clusterDim.z = 1;
+        ++num_attrs;
     }
-    CKL_TRY_CUDA(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<kMode, OutT>, ta, tb, tc, p));
-    if (p.sched.sk_tiles > 0) {
+    cfg.attrs = attrs;
+    cfg.numAttrs = num_attrs;
+    if (p.sched.sk_tiles > 0 && p.sk_flags != nullptr) {
+        // Fused stream-K: CTAs of this launch wait for partials of other CTAs, so the whole
+        // grid must be resident at once: cooperative launch.  If the device cannot promise
+        // that, fall through to the two-kernel form, where nobody waits for anybody.
+        attrs[num_attrs].id = cudaLaunchAttributeCooperative;
+        attrs[num_attrs].val.cooperative = 1;
+        cfg.numAttrs = num_attrs + 1;
+        if (cudaLaunchKernelEx(&cfg, umma_gemm_kernel<kMode, OutT>, ta, tb, tc, p) == cudaSuccess) {
+            return CKL_OK;
+        }
+        (void)cudaGetLastError();
+        cfg.numAttrs = num_attrs;
+    }
+    GemmParams q = p;
+    q.sk_flags = nullptr;
+    CKL_TRY_CUDA(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<kMode, OutT>, ta, tb, tc, q));
+    if (q.sched.sk_tiles > 0) {
         streamk_fixup_kernel<Cfg::kTileM, Cfg::kTileN, OutT>
-            <<<dim3(static_cast<unsigned>(p.sched.sk_tiles), Cfg::kTileM / 32 * Cfg::kNHalves), 256, 0,
-               stream>>>(p);
+            <<<dim3(static_cast<unsigned>(q.sched.sk_tiles), Cfg::kTileM / 32 * Cfg::kNHalves), 256, 0,
+               stream>>>(q);
         CKL_TRY_CUDA(cudaGetLastError());
     }
     return CKL_OK;
@@ -572,9 +619,23 @@ int gemm_impl(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, 
     }
 #endif
     if (plan.workspace_bytes > 0) {
-        if (const int rc = get_workspace(ctx, stream, plan.workspace_bytes, &p.workspace);
+        unsigned int* flags = nullptr;
+        unsigned int epoch = 0;
+        if (const int rc = get_workspace(ctx, stream, plan.workspace_bytes, &p.workspace, &flags, &epoch);
             rc != CKL_OK) {
             return rc;
+        }
+        // CKL_STREAMK_FIXUP=pass keeps the separate fix-up kernel (for comparisons).
+        static const bool two_pass = [] {
+            const char* v = std::getenv("CKL_STREAMK_FIXUP");
+            return v != nullptr && std::strcmp(v, "pass") == 0;
+        }();
+        // Fused where every unit has whole tiles left after its stream-K range, so the
+        // reduction hides behind them; a launch that is all stream-K ends with the reduction
+        // either way, and there the fix-up pass, spread over the whole GPU, measured faster.
+        if (!two_pass && plan.sched.dp_tiles >= plan.sched.units) {
+            p.sk_flags = flags;
+            p.sk_epoch = epoch;
         }
     }
     switch (c_dtype) {

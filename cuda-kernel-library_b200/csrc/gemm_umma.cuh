@@ -56,6 +56,8 @@ struct GemmParams {
     void* c;              // output, OutT, row-major, leading dimension ldc
     const float* bias;    // n floats (kEpiBiasRelu) or nullptr
     float* workspace;     // partial-tile slots (stream-K) or nullptr
+    unsigned int* sk_flags;  // fused stream-K: one word per (slot, 32-row group, half), or nullptr
+    unsigned int sk_epoch;   // value a flag takes when its part of a partial is complete
     unsigned int* status; // 4 words: code, block, role, detail
     int m, n, k;
     int ldc;
@@ -184,6 +186,32 @@ __device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, cons
             }
         }
     }
+}
+
+// Bounded wait for a flag word another CTA of the same launch publishes (fused stream-K).
+// The writer never waits for the reader, so the wait ends as soon as the writer has run;
+// the limit only guards against a writer that gave up.
+__device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int value,
+                                          const Control& ctl, unsigned int role,
+                                          unsigned int detail_word) {
+    unsigned long long t0 = 0;
+    unsigned int spins = 0;
+    while (ptx::ld_acquire_gpu(flag) != value) {
+        __nanosleep(200);
+        if ((++spins & 63u) == 0u) {
+            if (*ctl.abort_flag != 0) {
+                return false;
+            }
+            const unsigned long long now = ptx::global_timer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > kWaitLimitNs) {
+                raise_abort(ctl, role, detail_word);
+                return false;
+            }
+        }
+    }
+    return true;
 }
 
 // Short bounded wait used only while draining on the way out: never raises.
@@ -607,7 +635,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t phase = 0;
             uint32_t seg_count = 0;
             bool ok = true;
+#ifdef CKL_EXPERIMENT
+            unsigned long long tl_sk_start = 0;
+#endif
             while (ok && next_segment(sched, &cur, &seg)) {
+#ifdef CKL_EXPERIMENT
+                if (tl_sk_start == 0 && seg.tile >= sched.dp_tiles) tl_sk_start = ptx::global_timer_ns();
+#endif
                 // Two accumulators, used alternately (kAccStages == 2), or one accumulator
                 // of two 256-column halves that the epilogue hands back one by one.
                 const uint32_t acc = kWide ? 0u : (seg_count & 1u);
@@ -724,6 +758,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 p.prof[blockIdx.x * 8 + 0] = static_cast<unsigned long long>(clock64() - prof_c0);
                 p.prof[blockIdx.x * 8 + 5] = static_cast<unsigned long long>(prof_wait2);
                 p.prof[blockIdx.x * 8 + 6] = it;
+                if (p.debug & 16) {
+                    p.prof[blockIdx.x * 8 + 1] = prof_entry;
+                    p.prof[blockIdx.x * 8 + 2] = tl_sk_start;
+                    p.prof[blockIdx.x * 8 + 3] = ptx::global_timer_ns();
+                }
             }
 #endif
             if (ok) {
@@ -795,8 +834,43 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const int row0 = row - static_cast<int>(lane);  // first row of this warp
             const int col_base = tn * Cfg::kTileN + static_cast<int>(half) * 256;
             const uint32_t t_row = tmem_base + ((quad * 32u) << 16) + acc_cols;
-            const bool tma_path = (p.c_tma != 0) && seg.slot < 0;
+            // A split tile is finished either by the separate fix-up pass (every unit parks its
+            // partial) or, fused, by the unit that holds the tile's first k blocks: that unit
+            // runs them last, so the others' partials are already in the workspace.
+            const bool fused = p.sk_flags != nullptr;
+            const bool owner = fused && seg.slot >= 0 && seg.kb_begin == 0;
+            const bool parks = seg.slot >= 0 && !owner;
+            const bool tma_path = (p.c_tma != 0) && !parks;
             const bool warp_has_rows = row0 < p.m;
+            const int group = row_in_tile >> 5;  // 32-row group of the tile this warp drains
+            const size_t slot_part = static_cast<size_t>(group * Cfg::kNHalves + static_cast<int>(half)) * 8192u +
+                                     lane * 4u;  // this lane's offset inside any slot
+            // The other holders of an owned tile are the next units, each with its first slot.
+            int peers = 0;
+            if (owner) {
+                const long long tile_end =
+                    static_cast<long long>(seg.tile - sched.dp_tiles + 1) * sched.k_blocks;
+                while (unit + 1 + peers < sched.units &&
+                       sk_range_begin(sched, unit + 1 + peers) < tile_end) {
+                    ++peers;
+                }
+            }
+            // Adds the peers' partials of one 32-column chunk, in ascending unit order.
+            auto add_partials = [&](int chunk32, uint32_t* r) {
+                for (int v = 0; v < peers; ++v) {
+                    const float* src = p.workspace +
+                                       static_cast<size_t>(2 * (unit + 1 + v)) * Cfg::kSlotFloats +
+                                       slot_part + chunk32 * 1024;
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        const float4 t = __ldcg(reinterpret_cast<const float4*>(src + q * 128));
+                        r[4 * q + 0] = __float_as_uint(__uint_as_float(r[4 * q + 0]) + t.x);
+                        r[4 * q + 1] = __float_as_uint(__uint_as_float(r[4 * q + 1]) + t.y);
+                        r[4 * q + 2] = __float_as_uint(__uint_as_float(r[4 * q + 2]) + t.z);
+                        r[4 * q + 3] = __float_as_uint(__uint_as_float(r[4 * q + 3]) + t.w);
+                    }
+                }
+            };
 
             // Hands the accumulator back to the MMA warp, once per tile: called as soon as
             // the last TMEM load of the tile has completed.
@@ -854,19 +928,47 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ptx::tc_fence_after_sync();
 
 #ifdef CKL_EXPERIMENT
+            const unsigned long long tl_w0 = ptx::global_timer_ns();
+#endif
+            if (peers > 0) {
+                // Wait (bounded) until every peer's warp of the same rows and columns has parked
+                // its partial.  Each lane then reads the flags itself, so that its loads of the
+                // partials are ordered after the writers' release.
+                int got = 1;
+                if (lane == 0) {
+                    for (int v = 0; v < peers && got; ++v) {
+                        const unsigned int* flag =
+                            p.sk_flags + static_cast<size_t>(2 * (unit + 1 + v)) * 16 + group * 2 + half;
+                        got = detail::wait_flag(flag, p.sk_epoch, ctl, kRoleEpilogue,
+                                                0x50000000u | static_cast<unsigned int>(unit + 1 + v))
+                                  ? 1
+                                  : 0;
+                    }
+                }
+                got = __shfl_sync(0xFFFFFFFFu, got, 0);
+                if (!got) {
+                    break;
+                }
+                for (int v = 0; v < peers; ++v) {
+                    const unsigned int* flag =
+                        p.sk_flags + static_cast<size_t>(2 * (unit + 1 + v)) * 16 + group * 2 + half;
+                    for (int i = 0; i < 1024 && ptx::ld_acquire_gpu(flag) != p.sk_epoch; ++i) {
+                    }
+                }
+            }
+
+#ifdef CKL_EXPERIMENT
+            ep_cw += static_cast<long long>(ptx::global_timer_ns() - tl_w0);
             if (p.debug & 4) {
             } else
 #endif
-            if (seg.slot >= 0) {
+            if (parks) {
                 // Partial accumulator -> FP32 workspace slot, whole tile, no predication.  The
                 // slot is not row-major: it is the image of the registers, laid out as
                 // [32-row group][256-column half][32-column chunk][4-column unit][lane][4],
                 // so every store (and every load of the fix-up pass, which uses the same
                 // lane = row mapping) moves 512 contiguous bytes per warp.
-                const int group = row_in_tile >> 5;
-                float* dst = p.workspace + static_cast<size_t>(seg.slot) * Cfg::kSlotFloats +
-                             static_cast<size_t>(group * Cfg::kNHalves + static_cast<int>(half)) * 8192u +
-                             lane * 4u;
+                float* dst = p.workspace + static_cast<size_t>(seg.slot) * Cfg::kSlotFloats + slot_part;
 #pragma unroll 1
                 for (int c = 0; c < 256 / 32; ++c) {
                     uint32_t r[32];
@@ -876,6 +978,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     for (int q = 0; q < 8; ++q) {
                         *reinterpret_cast<uint4*>(dst + c * 1024 + q * 128) =
                             make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                    }
+                }
+                if (fused) {
+                    // publish: this warp's part of the slot is complete
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::st_release_gpu(
+                            p.sk_flags + static_cast<size_t>(seg.slot) * 16 + group * 2 + half, p.sk_epoch);
                     }
                 }
             } else if (tma_path) {
@@ -1002,6 +1113,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     if (c + 1 == n_chunks) {
                         release_acc();  // the last columns are in registers
                     }
+                    if (peers > 0) {
+#pragma unroll
+                        for (int h = 0; h < kChunkCols / 32; ++h) {
+                            add_partials(c * (kChunkCols / 32) + h, r + h * 32);
+                        }
+                    }
                     CKL_EP(ep_ld);
                     alive = finish_chunk(c, r);
                 }
@@ -1019,6 +1136,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     uint32_t r[32];
                     ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), r);
                     ptx::tmem_ld_wait();
+                    if (peers > 0) {
+                        add_partials(c, r);
+                    }
                     if (row_ok) {
                         float acc_f[32];
 #pragma unroll
@@ -1039,7 +1159,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ++seg_count;
         }
 #ifdef CKL_EXPERIMENT
-        if (p.prof && ew == 0 && lane == 0) {
+        if (p.prof && ew == 0 && lane == 0 && (p.debug & 16)) {
+            p.prof[blockIdx.x * 8 + 4] = ptx::global_timer_ns();
+            p.prof[blockIdx.x * 8 + 7] = static_cast<unsigned long long>(ep_cw);
+        } else if (p.prof && ew == 0 && lane == 0) {
             p.prof[blockIdx.x * 8 + 1] = static_cast<unsigned long long>(ep_ld);
             p.prof[blockIdx.x * 8 + 2] = static_cast<unsigned long long>(ep_cw);
             p.prof[blockIdx.x * 8 + 3] = static_cast<unsigned long long>(ep_ci);

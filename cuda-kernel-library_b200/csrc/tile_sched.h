@@ -6,15 +6,16 @@
 // k_blocks pipeline steps.  `units` schedulable workers (one CTA, or one CTA
 // pair for the 2-CTA kernel) run persistently:
 //
-//   * data-parallel region: tiles [0, dp_tiles) are dealt round-robin; unit u
-//     computes tiles u, u + units, ... whole and writes C directly;
-//   * stream-K region: the remaining sk_tiles tiles are laid end to end as
-//     sk_tiles * k_blocks iterations and cut into `units` equal contiguous
+//   * stream-K region (run first): the last sk_tiles tiles are laid end to end
+//     as sk_tiles * k_blocks iterations and cut into `units` equal contiguous
 //     ranges.  A unit whose range covers a whole tile writes C directly; a
-//     range that starts or stops inside a tile yields a PARTIAL accumulator
-//     that goes to an FP32 workspace slot, and a separate fix-up pass adds the
-//     partials of each split tile in ascending unit order (deterministic) and
-//     applies alpha, beta and the output cast.
+//     range that starts or stops inside a tile yields a PARTIAL accumulator.
+//     The partials of a split tile are added in ascending unit order
+//     (deterministic) either by the unit that holds the tile's first k blocks
+//     (fused: the others park their partials in FP32 workspace slots and raise
+//     a flag) or by a separate fix-up pass over parked partials of all holders;
+//   * data-parallel region (run after): tiles [0, dp_tiles) are dealt
+//     round-robin; unit u computes tiles u, u + units, ... whole.
 //
 // The reference has no counterpart: it launches one CTA per tile and leaves
 // the last wave under-filled (src/gemm/gemm_mma_opt.cu:223-225).
@@ -85,15 +86,10 @@ CKL_HD SegmentCursor make_cursor(const Schedule& s, int u) {
     return c;
 }
 
+// The stream-K range comes FIRST, the unit's whole tiles after it: a unit that has to wait
+// for other units' partials and add them (fused fix-up) does so while its MMA warp is already
+// busy with the whole tiles, and the launch ends with an ordinary tile, not with a reduction.
 CKL_HD bool next_segment(const Schedule& s, SegmentCursor* c, Segment* out) {
-    if (c->dp_next < s.dp_tiles) {
-        out->tile = c->dp_next;
-        out->kb_begin = 0;
-        out->kb_end = s.k_blocks;
-        out->slot = -1;
-        c->dp_next += s.units;
-        return true;
-    }
     if (c->sk_cur < c->sk_end) {
         const long long t = c->sk_cur / s.k_blocks;
         const int kb0 = static_cast<int>(c->sk_cur - t * s.k_blocks);
@@ -113,6 +109,14 @@ CKL_HD bool next_segment(const Schedule& s, SegmentCursor* c, Segment* out) {
             out->slot = 2 * c->unit + (kb0 == 0 ? 1 : 0);
         }
         c->sk_cur = stop;
+        return true;
+    }
+    if (c->dp_next < s.dp_tiles) {
+        out->tile = c->dp_next;
+        out->kb_begin = 0;
+        out->kb_end = s.k_blocks;
+        out->slot = -1;
+        c->dp_next += s.units;
         return true;
     }
     return false;

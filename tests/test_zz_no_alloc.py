@@ -60,6 +60,24 @@ def test_noalloc_entry_matches_regular_entry_twice(ckl, orc):
         torch.cuda.synchronize()
         ckl.device_status()
         _compare(ckl, orc, got, want, k, cdt, f"{m}x{n}x{k}")
+    # One full wave of whole tiles plus a split remainder: the regular entry point adds the
+    # partials inside the GEMM kernel (the unit holding a tile's first k blocks does it), this one
+    # in the separate fix-up pass.  Both add in ascending unit order: the bits must agree.
+    m, n, k = 2048, 2816, 2048
+    plan = ckl.plan_gemm(m, n, k, algo=ckl.ALGO_UMMA_SK)
+    assert plan.sk_tiles > 0 and plan.dp_tiles >= plan.units
+    a = torch.from_numpy(orc.narrow(orc.random_matrix(m, k, 31), ckl.BF16).view(np.int16)) \
+        .view(torch.bfloat16).cuda()
+    b = torch.from_numpy(orc.narrow(orc.random_matrix(k, n, 32), ckl.BF16).view(np.int16)) \
+        .view(torch.bfloat16).cuda()
+    c0 = torch.from_numpy(orc.random_matrix(m, n, 33)).cuda()
+    want, got = c0.clone(), c0.clone()
+    ckl.gemm_ex(ckl.BF16, a, b, want, ckl.F32, m, n, k, k, n, n, 1.0, 0.5, ckl.ALGO_UMMA_SK)
+    ckl.gemm_streamk_noalloc(ckl.BF16, a, b, got, ckl.F32, m, n, k, k, n, n, 1.0, 0.5)
+    torch.cuda.synchronize()
+    ckl.device_status()
+    assert torch.equal(got, want)
+    _compare(ckl, orc, got, want, k, ckl.F32, f"{m}x{n}x{k}")
     # shapes the tensor-core kernel cannot take are refused, not computed some other way
     with pytest.raises(ckl.CklError) as e:
         ckl.gemm_streamk_noalloc(ckl.F16, a, b, got, ckl.F32, 129, 257, 193, 193, 257, 257, 1.0, 0.0)
