@@ -75,7 +75,12 @@ struct DeviceCtx {
     unsigned int* status = nullptr;            // 4 words on the device
     std::map<cudaStream_t, Staging> workspace; // stream-K partial slots, one per stream
     Staging host_a, host_b, host_c;            // device staging for ckl_gemm_host
-    cudaStream_t host_stream = nullptr;
+    cudaStream_t host_stream = nullptr;        // ckl_gemm_host: compute
+    cudaStream_t host_in = nullptr;            // ckl_gemm_host: host -> device copies
+    cudaStream_t host_out = nullptr;           // ckl_gemm_host: device -> host copies
+    static constexpr int kHostPanels = 16;
+    cudaEvent_t host_events[2 * kHostPanels] = {};  // per panel: uploaded, computed
+    std::mutex host_mu;                        // one ckl_gemm_host call at a time per device
     bool attrs_set = false;
     std::mutex mu;
 };
@@ -832,36 +837,89 @@ int ckl_gemm_host(int ab_dtype, const void* a_host, const void* b_host, void* c_
     if (const int rc = get_ctx(&ctx); rc != CKL_OK) {
         return rc;
     }
+    std::lock_guard<std::mutex> one_call(ctx->host_mu);  // the staging buffers are shared
     std::unique_lock<std::mutex> lock(ctx->mu);
     if (ctx->host_stream == nullptr) {
         CKL_TRY_CUDA(cudaStreamCreateWithFlags(&ctx->host_stream, cudaStreamNonBlocking));
+        CKL_TRY_CUDA(cudaStreamCreateWithFlags(&ctx->host_in, cudaStreamNonBlocking));
+        CKL_TRY_CUDA(cudaStreamCreateWithFlags(&ctx->host_out, cudaStreamNonBlocking));
+        for (cudaEvent_t& e : ctx->host_events) {
+            CKL_TRY_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        }
     }
-    const size_t a_bytes = static_cast<size_t>(m) * std::max(k, 0) * 2;
-    const size_t b_bytes = static_cast<size_t>(std::max(k, 0)) * n * 2;
-    const size_t c_bytes = static_cast<size_t>(m) * n * dtype_size(c_dtype);
+    const size_t kk = static_cast<size_t>(std::max(k, 0));
+    const size_t csz = dtype_size(c_dtype);
+    const size_t a_bytes = static_cast<size_t>(m) * kk * 2;
+    const size_t b_bytes = kk * n * 2;
+    const size_t c_bytes = static_cast<size_t>(m) * n * csz;
     if (int rc = ensure_staging(&ctx->host_a, std::max<size_t>(a_bytes, 16)); rc != CKL_OK) return rc;
     if (int rc = ensure_staging(&ctx->host_b, std::max<size_t>(b_bytes, 16)); rc != CKL_OK) return rc;
     if (int rc = ensure_staging(&ctx->host_c, c_bytes); rc != CKL_OK) return rc;
-    cudaStream_t s = ctx->host_stream;
-    if (a_bytes > 0) {
-        CKL_TRY_CUDA(cudaMemcpyAsync(ctx->host_a.ptr, a_host, a_bytes, cudaMemcpyHostToDevice, s));
-    }
+    // The call is bound by the host link, which carries both directions at once: B goes up
+    // first, then A and C travel in row panels, and panel i is multiplied and sent back while
+    // panel i+1 is still on its way up.  Three streams (up, compute, down) chained by events.
+    constexpr int kMaxPanels = DeviceCtx::kHostPanels;
+    const int panels = std::max(1, std::min(kMaxPanels, m / 1024));
+    const int rows_per_panel = ((m + panels - 1) / panels + 255) / 256 * 256;
+    cudaStream_t s_in = ctx->host_in, s = ctx->host_stream, s_out = ctx->host_out;
     if (b_bytes > 0) {
-        CKL_TRY_CUDA(cudaMemcpyAsync(ctx->host_b.ptr, b_host, b_bytes, cudaMemcpyHostToDevice, s));
+        CKL_TRY_CUDA(cudaMemcpyAsync(ctx->host_b.ptr, b_host, b_bytes, cudaMemcpyHostToDevice, s_in));
     }
-    if (beta != 0.0f) {
-        CKL_TRY_CUDA(cudaMemcpyAsync(ctx->host_c.ptr, c_host, c_bytes, cudaMemcpyHostToDevice, s));
-    }
-    // gemm_impl takes ctx->mu only inside get_workspace; release ours first.
+    auto* dev_a = static_cast<unsigned char*>(ctx->host_a.ptr);
+    auto* dev_c = static_cast<unsigned char*>(ctx->host_c.ptr);
+    const auto* src_a = static_cast<const unsigned char*>(a_host);
+    auto* host_c = static_cast<unsigned char*>(c_host);
+    void* dev_b = ctx->host_b.ptr;
+    // gemm_impl takes ctx->mu inside get_workspace; release ours while it runs.
     lock.unlock();
-    const int rc = gemm_impl(ab_dtype, ctx->host_a.ptr, ctx->host_b.ptr, ctx->host_c.ptr, c_dtype,
-                             nullptr, m, n, k, k, n, n, alpha, beta, kEpiLinear, CKL_ALGO_AUTO, s);
-    lock.lock();
+    int rc = CKL_OK;
+    auto cuda_ok = [&rc](cudaError_t e, const char* what) {
+        if (e != cudaSuccess && rc == CKL_OK) {
+            rc = fail(CKL_ERR_CUDA, "ckl_gemm_host: %s failed: %s", what, cudaGetErrorString(e));
+        }
+        return rc == CKL_OK;
+    };
+    int used = 0;
+    for (int row0 = 0; row0 < m && rc == CKL_OK; row0 += rows_per_panel, ++used) {
+        const int rows = std::min(rows_per_panel, m - row0);
+        const size_t a_off = static_cast<size_t>(row0) * kk * 2;
+        const size_t c_off = static_cast<size_t>(row0) * n * csz;
+        const size_t c_panel = static_cast<size_t>(rows) * n * csz;
+        cudaEvent_t up = ctx->host_events[2 * used], done = ctx->host_events[2 * used + 1];
+        if (kk > 0 && !cuda_ok(cudaMemcpyAsync(dev_a + a_off, src_a + a_off, static_cast<size_t>(rows) * kk * 2,
+                                               cudaMemcpyHostToDevice, s_in), "copy of A")) {
+            break;
+        }
+        if (beta != 0.0f && !cuda_ok(cudaMemcpyAsync(dev_c + c_off, host_c + c_off, c_panel,
+                                                     cudaMemcpyHostToDevice, s_in), "copy of C")) {
+            break;
+        }
+        if (!cuda_ok(cudaEventRecord(up, s_in), "event record") ||
+            !cuda_ok(cudaStreamWaitEvent(s, up, 0), "stream wait")) {
+            break;
+        }
+        rc = gemm_impl(ab_dtype, dev_a + a_off, dev_b, dev_c + c_off, c_dtype, nullptr, rows, n, k, k, n, n,
+                       alpha, beta, kEpiLinear, CKL_ALGO_AUTO, s);
+        if (rc != CKL_OK) {
+            break;
+        }
+        if (!cuda_ok(cudaEventRecord(done, s), "event record") ||
+            !cuda_ok(cudaStreamWaitEvent(s_out, done, 0), "stream wait") ||
+            !cuda_ok(cudaMemcpyAsync(host_c + c_off, dev_c + c_off, c_panel, cudaMemcpyDeviceToHost, s_out),
+                     "copy of the result")) {
+            break;
+        }
+    }
+    // Nothing of this call may still be in flight when it returns, whatever happened above.
+    const cudaError_t e_in = cudaStreamSynchronize(s_in);
+    const cudaError_t e_run = cudaStreamSynchronize(s);
+    const cudaError_t e_out = cudaStreamSynchronize(s_out);
     if (rc != CKL_OK) {
         return rc;
     }
-    CKL_TRY_CUDA(cudaMemcpyAsync(c_host, ctx->host_c.ptr, c_bytes, cudaMemcpyDeviceToHost, s));
-    CKL_TRY_CUDA(cudaStreamSynchronize(s));
+    CKL_TRY_CUDA(e_in);
+    CKL_TRY_CUDA(e_run);
+    CKL_TRY_CUDA(e_out);
     return CKL_OK;
 }
 
@@ -1086,6 +1144,11 @@ void ckl_shutdown(void) {
         cudaFree(ctx->status);
         if (ctx->host_stream != nullptr) {
             cudaStreamDestroy(ctx->host_stream);
+            cudaStreamDestroy(ctx->host_in);
+            cudaStreamDestroy(ctx->host_out);
+            for (cudaEvent_t e : ctx->host_events) {
+                cudaEventDestroy(e);
+            }
         }
     }
     g_ctx.clear();

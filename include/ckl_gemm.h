@@ -122,7 +122,9 @@ int ckl_strsm_lower(const float* l, float* b, int m, int n, int lda, int ldb, fl
  * This is what a caller holding host matrices pays end to end; it is the
  * host-side counterpart of the upload / launch / download sequence in the
  * reference's test driver (tests/test_gemm_tensor.cpp:69-85).  Pinned host
- * buffers make the copies run at full PCIe rate. */
+ * buffers make the copies run at full link rate.  Large problems travel in row
+ * panels so that uploads, the multiplication and downloads overlap; one call
+ * at a time per device (calls from several threads queue). */
 int ckl_gemm_host(int ab_dtype, const void* a_host, const void* b_host, void* c_host, int c_dtype,
                   int m, int n, int k, float alpha, float beta);
 

@@ -409,6 +409,27 @@ def test_host_buffer_call(env):
     env.gate(got, ref, k, ckl.BF16, "host buffers")
 
 
+def test_host_buffer_call_in_row_panels(env):
+    """Large enough that the host call travels in several row panels (ragged last one): the
+    result must equal what one device-buffer call on the same inputs gives."""
+    ckl, orc = env.ckl, env.orc
+    m, n, k = 3300, 768, 512
+    abits = orc.narrow(orc.random_matrix(m, k, 41), ckl.F16)
+    bbits = orc.narrow(orc.random_matrix(k, n, 42), ckl.F16)
+    c0 = orc.random_matrix(m, n, 43)
+    ha = torch.from_numpy(abits.view(np.int16)).pin_memory()
+    hb = torch.from_numpy(bbits.view(np.int16)).pin_memory()
+    hc = torch.from_numpy(c0.copy()).pin_memory()
+    ckl.gemm_host(ckl.F16, ha.data_ptr(), hb.data_ptr(), hc.data_ptr(), ckl.F32, m, n, k, 1.25, -0.5)
+    da, db = env.to_dev16(abits, ckl.F16), env.to_dev16(bbits, ckl.F16)
+    dc = torch.from_numpy(c0).cuda()
+    ckl.gemm_ex(ckl.F16, da, db, dc, ckl.F32, m, n, k, k, n, n, 1.25, -0.5)
+    torch.cuda.synchronize()
+    ref, _ = orc.gemm_reference_mt(orc.widen(abits, ckl.F16), orc.widen(bbits, ckl.F16), c0, 1.25, -0.5)
+    env.gate(hc.numpy(), ref, k, ckl.F32, "host buffers, 3 panels")
+    assert orc.relative_frobenius_error(hc.numpy(), dc.cpu().numpy().astype(np.float64)) < 1e-6
+
+
 def test_assemble_column_blocks(env):
     ckl = env.ckl
     for dtype, width in [(torch.bfloat16, 1024), (torch.float32, 20), (torch.float16, 7)]:
