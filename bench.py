@@ -204,7 +204,7 @@ def run_reference_arm(args) -> None:
                 "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def workload_config(gpus: int, algo: str) -> dict:
@@ -401,7 +401,7 @@ def run_ours(args) -> None:
                 "kind": kind,
                 "sample": f"{rows} of the 8192 rows of C (all 8192 columns, K = 8192), one pass of "
                           "the reference's single-threaded ckl::gemm_reference"}
-        print(json.dumps(line), flush=True)
+        emit(line)
 
     if world > 1:
         dist.destroy_process_group()
@@ -411,6 +411,29 @@ def free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         return s.getsockname()[1]
+
+
+_RESULT_FD = None
+
+
+def keep_stdout_for_the_result() -> None:
+    """The contract is ONE JSON line on stdout.  Libraries may write there too (NCCL prints its
+    version line to stdout when NCCL_DEBUG is set in the environment), so file descriptor 1 is
+    pointed at stderr for the whole run and the result goes to a saved copy of the original."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
 
 
 def main() -> None:
@@ -423,6 +446,8 @@ def main() -> None:
                     help="pin a kernel (auto, simt, umma_1cta, umma_1cta_streamk, umma_2cta, "
                          "umma_2cta_streamk); the default is what every caller gets")
     args = ap.parse_args()
+    if args.gpus <= 1 or "WORLD_SIZE" in os.environ:
+        keep_stdout_for_the_result()   # (the torchrun re-launch below passes its child's stdout through)
     if args.impl == "reference":
         run_reference_arm(args)
         return
