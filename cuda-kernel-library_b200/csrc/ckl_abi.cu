@@ -32,8 +32,8 @@ namespace {
 using namespace ckl;
 
 thread_local std::string g_last_error;
-#ifdef CKL_EXPERIMENT
-unsigned long long* g_prof_buf = nullptr;
+#ifdef CKL_TIMERS
+unsigned long long* g_timer_buf = nullptr;  // instrumented builds: counters of the last launch
 #endif
 
 int fail(int code, const char* fmt, ...) {
@@ -610,17 +610,15 @@ int gemm_impl(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, 
     p.idesc = ptx::make_idesc_f16(ab_dtype == CKL_F16 ? 0u : 1u, 0u, 1u, plan.pair ? 256u : 128u,
                                   256u);
     p.sched = plan.sched;
-#ifdef CKL_EXPERIMENT
-    p.debug = getenv("CKL_DEBUG") ? atoi(getenv("CKL_DEBUG")) : 0;
-    if (getenv("CKL_GROUP_M")) p.sched.group_m = atoi(getenv("CKL_GROUP_M"));
+#ifdef CKL_TIMERS
     {
-        static unsigned long long* prof_buf = nullptr;
-        if (prof_buf == nullptr) {
-            cudaMalloc(&prof_buf, 1024 * 8 * sizeof(unsigned long long));
+        const char* mode = std::getenv("CKL_TIMER_MODE");
+        p.timer_mode = mode != nullptr ? std::atoi(mode) : 0;
+        if (g_timer_buf == nullptr) {
+            cudaMalloc(&g_timer_buf, 1024 * 8 * sizeof(unsigned long long));
         }
-        cudaMemsetAsync(prof_buf, 0, 1024 * 8 * sizeof(unsigned long long), stream);
-        p.prof = prof_buf;
-        g_prof_buf = prof_buf;
+        cudaMemsetAsync(g_timer_buf, 0, 1024 * 8 * sizeof(unsigned long long), stream);
+        p.timers = g_timer_buf;
     }
 #endif
     if (plan.workspace_bytes > 0) {
@@ -1100,12 +1098,14 @@ int ckl_stream_copy(void* dst, const void* src, size_t bytes, ckl_stream_t strea
     return CKL_OK;
 }
 
-#ifdef CKL_EXPERIMENT
-int ckl_exp_read_prof(unsigned long long* out, int ctas) {
+#ifdef CKL_TIMERS
+// Instrumented builds only: waits for the device and copies the counters of the last launch
+// (eight per CTA) to `out`.
+int ckl_read_timers(unsigned long long* out, int ctas) {
     cudaDeviceSynchronize();
-    return g_prof_buf ? static_cast<int>(cudaMemcpy(out, g_prof_buf, sizeof(unsigned long long) * 8 * ctas,
-                                                    cudaMemcpyDeviceToHost))
-                      : -1;
+    return g_timer_buf ? static_cast<int>(cudaMemcpy(out, g_timer_buf, sizeof(unsigned long long) * 8 * ctas,
+                                                     cudaMemcpyDeviceToHost))
+                       : -1;
 }
 #endif
 

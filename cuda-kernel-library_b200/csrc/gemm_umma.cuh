@@ -67,9 +67,11 @@ struct GemmParams {
     int epi_mode;
     uint32_t idesc;
     Schedule sched;
-#ifdef CKL_EXPERIMENT
-    int debug;  // experiment builds only: 1 = no TMA, 2 = no MMA, 4 = no epilogue traffic
-    unsigned long long* prof;  // experiment builds only: 8 counters per CTA
+#ifdef CKL_TIMERS
+    // Instrumented builds only (-DCKL_TIMERS, see kernel_timers.py): eight counters per CTA.
+    // timer_mode 0: cycles per epilogue phase; 1: wall-clock timeline of a stream-K launch.
+    int timer_mode;
+    unsigned long long* timers;
 #endif
 };
 
@@ -403,7 +405,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     constexpr bool kPair = Cfg::kPair;
     constexpr bool kWide = Cfg::kWide;
     constexpr int kStages = Cfg::kStages;
-#ifdef CKL_EXPERIMENT
+#ifdef CKL_TIMERS
     const unsigned long long prof_entry = ptx::global_timer_ns();
 #endif
 
@@ -487,7 +489,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t tmem_base = *tmem_slot_ptr;
 
     const Schedule& sched = p.sched;
-#ifdef CKL_EXPERIMENT
+#ifdef CKL_TIMERS
     const long long prof_c0 = clock64();
     const unsigned long long prof_t0 = ptx::global_timer_ns();
     long long prof_wait = 0, prof_wait2 = 0;
@@ -504,12 +506,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // TMA producer.
             SegmentCursor cur = make_cursor(sched, unit);
             Segment seg;
-#ifdef CKL_EXPERIMENT
-            const uint64_t hints[3] = {ptx::kL2EvictNormal, ptx::kL2EvictFirst, ptx::kL2EvictLast};
-            const uint64_t hint_a = hints[(p.debug >> 8) & 3], hint_b = hints[(p.debug >> 10) & 3];
-#else
             constexpr uint64_t hint_a = ptx::kL2EvictNormal, hint_b = ptx::kL2EvictNormal;
-#endif
             uint32_t it = 0;       // k blocks issued so far
             int stage = 0;         // it % kStages
             uint32_t phase = 0;    // (it / kStages) & 1
@@ -532,11 +529,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     }
                     const uint32_t a_dst = ring + static_cast<uint32_t>(stage) * Cfg::kStageBytes;
                     const uint32_t b_dst = a_dst + Cfg::kABytes;
-#ifdef CKL_EXPERIMENT
-                    if (p.debug & 1) {
-                        if (!kPair || leader) ptx::mbar_arrive(full_bar(stage));
-                    } else
-#endif
                     {
                         uint32_t bar = full_bar(stage);
                         if constexpr (kPair) {
@@ -635,11 +627,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t phase = 0;
             uint32_t seg_count = 0;
             bool ok = true;
-#ifdef CKL_EXPERIMENT
+#ifdef CKL_TIMERS
             unsigned long long tl_sk_start = 0;
 #endif
             while (ok && next_segment(sched, &cur, &seg)) {
-#ifdef CKL_EXPERIMENT
+#ifdef CKL_TIMERS
                 if (tl_sk_start == 0 && seg.tile >= sched.dp_tiles) tl_sk_start = ptx::global_timer_ns();
 #endif
                 // Two accumulators, used alternately (kAccStages == 2), or one accumulator
@@ -689,16 +681,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         next_stage = 0;
                         next_phase ^= 1u;
                     }
-#ifdef CKL_EXPERIMENT
-                    if (p.debug & 2) {
-                        ptx::mbar_arrive(empty_bar(stage));
-                        if (kPair) ptx::mbar_arrive_cluster(ptx::map_to_cta(empty_bar(stage), 1));
-                        ++it;
-                        stage = next_stage;
-                        phase = next_phase;
-                        continue;
-                    }
-#endif
                     ready = false;
 #pragma unroll
                     for (int j = 0; j < 4 * Cfg::kKSub; ++j) {
@@ -735,14 +717,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     stage = next_stage;
                     phase = next_phase;
                 }
-#ifdef CKL_EXPERIMENT
-                if (ok && (p.debug & 2)) {
-                    ptx::mbar_arrive(acc_full_bar(acc));
-                    if (kPair) ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_full_bar(acc), 1));
-                    ++seg_count;
-                    continue;
-                }
-#endif
                 if (ok) {
                     if constexpr (kPair) {
                         ptx::umma_commit_pair(acc_full_bar(acc));
@@ -753,15 +727,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     ++seg_count;
                 }
             }
-#ifdef CKL_EXPERIMENT
-            if (p.prof) {
-                p.prof[blockIdx.x * 8 + 0] = static_cast<unsigned long long>(clock64() - prof_c0);
-                p.prof[blockIdx.x * 8 + 5] = static_cast<unsigned long long>(prof_wait2);
-                p.prof[blockIdx.x * 8 + 6] = it;
-                if (p.debug & 16) {
-                    p.prof[blockIdx.x * 8 + 1] = prof_entry;
-                    p.prof[blockIdx.x * 8 + 2] = tl_sk_start;
-                    p.prof[blockIdx.x * 8 + 3] = ptx::global_timer_ns();
+#ifdef CKL_TIMERS
+            if (p.timers) {
+                p.timers[blockIdx.x * 8 + 0] = static_cast<unsigned long long>(clock64() - prof_c0);
+                p.timers[blockIdx.x * 8 + 5] = static_cast<unsigned long long>(prof_wait2);
+                p.timers[blockIdx.x * 8 + 6] = it;
+                if (p.timer_mode == 1) {
+                    p.timers[blockIdx.x * 8 + 1] = prof_entry;
+                    p.timers[blockIdx.x * 8 + 2] = tl_sk_start;
+                    p.timers[blockIdx.x * 8 + 3] = ptx::global_timer_ns();
                 }
             }
 #endif
@@ -816,7 +790,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const bool reads_c = (p.epi_mode == kEpiLinear) && (p.beta != 0.0f);
         const bool unit_alpha = p.alpha == 1.0f;
         bool alive = true;
-#ifdef CKL_EXPERIMENT
+#ifdef CKL_TIMERS
         long long ep_ld = 0, ep_cw = 0, ep_ci = 0, ep_cp = 0, ep_st = 0, ep_t = 0;
 #define CKL_EP(acc_) do { const long long n_ = clock64(); acc_ += n_ - ep_t; ep_t = n_; } while (0)
 #else
@@ -927,7 +901,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
             ptx::tc_fence_after_sync();
 
-#ifdef CKL_EXPERIMENT
+#ifdef CKL_TIMERS
             const unsigned long long tl_w0 = ptx::global_timer_ns();
 #endif
             if (peers > 0) {
@@ -957,10 +931,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
             }
 
-#ifdef CKL_EXPERIMENT
-            ep_cw += static_cast<long long>(ptx::global_timer_ns() - tl_w0);
-            if (p.debug & 4) {
-            } else
+#ifdef CKL_TIMERS
+            if (p.timer_mode == 1) {
+                ep_cw += static_cast<long long>(ptx::global_timer_ns() - tl_w0);
+            }
 #endif
             if (parks) {
                 // Partial accumulator -> FP32 workspace slot, whole tile, no predication.  The
@@ -1104,7 +1078,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 };
 #pragma unroll 1
                 for (int c = 0; c < n_chunks && alive; ++c) {
-#ifdef CKL_EXPERIMENT
+#ifdef CKL_TIMERS
                     ep_t = clock64();
 #endif
                     uint32_t r[kChunkCols];
@@ -1158,16 +1132,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             __syncwarp();
             ++seg_count;
         }
-#ifdef CKL_EXPERIMENT
-        if (p.prof && ew == 0 && lane == 0 && (p.debug & 16)) {
-            p.prof[blockIdx.x * 8 + 4] = ptx::global_timer_ns();
-            p.prof[blockIdx.x * 8 + 7] = static_cast<unsigned long long>(ep_cw);
-        } else if (p.prof && ew == 0 && lane == 0) {
-            p.prof[blockIdx.x * 8 + 1] = static_cast<unsigned long long>(ep_ld);
-            p.prof[blockIdx.x * 8 + 2] = static_cast<unsigned long long>(ep_cw);
-            p.prof[blockIdx.x * 8 + 3] = static_cast<unsigned long long>(ep_ci);
-            p.prof[blockIdx.x * 8 + 4] = static_cast<unsigned long long>(ep_cp);
-            p.prof[blockIdx.x * 8 + 7] = static_cast<unsigned long long>(ep_st);
+#ifdef CKL_TIMERS
+        if (p.timers && ew == 0 && lane == 0 && (p.timer_mode == 1)) {
+            p.timers[blockIdx.x * 8 + 4] = ptx::global_timer_ns();
+            p.timers[blockIdx.x * 8 + 7] = static_cast<unsigned long long>(ep_cw);
+        } else if (p.timers && ew == 0 && lane == 0) {
+            p.timers[blockIdx.x * 8 + 1] = static_cast<unsigned long long>(ep_ld);
+            p.timers[blockIdx.x * 8 + 2] = static_cast<unsigned long long>(ep_cw);
+            p.timers[blockIdx.x * 8 + 3] = static_cast<unsigned long long>(ep_ci);
+            p.timers[blockIdx.x * 8 + 4] = static_cast<unsigned long long>(ep_cp);
+            p.timers[blockIdx.x * 8 + 7] = static_cast<unsigned long long>(ep_st);
         }
 #endif
         if (lane == 0) {
