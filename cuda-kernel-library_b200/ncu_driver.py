@@ -41,9 +41,25 @@ def main() -> None:
     sys.modules["ckl_b200"] = ckl
     spec.loader.exec_module(ckl)
 
+    if args.algo == "sgemm":
+        # the FP32 CUDA-core kernel behind the reference's FP32 rungs (operands are FP32)
+        m, n, k = args.m, args.n, args.k
+        a = torch.randn(m, k, device="cuda")
+        b = torch.randn(k, n, device="cuda")
+        c = torch.randn(m, n, device="cuda")
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(args.iters):
+            e0.record()
+            ckl.sgemm(a, b, c, m, n, k, alpha=args.alpha, beta=args.beta)
+            e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        print(f"sgemm {m}x{n}x{k} fp32 beta={args.beta}: {ms:.4f} ms, "
+              f"{2.0 * m * n * k / ms / 1e9:.2f} TFLOP/s (last of {args.iters} launches)")
+        return
     algos = {ckl.algo_name(i): i for i in range(ckl.NUM_ALGOS)}
     if args.algo not in algos:
-        raise SystemExit(f"--algo must be one of {sorted(algos)}")
+        raise SystemExit(f"--algo must be one of {sorted(algos) + ['sgemm']}")
     tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
     cdt = {"f16": ckl.F16, "bf16": ckl.BF16, "f32": ckl.F32}
     m, n, k = args.m, args.n, args.k

@@ -1,0 +1,104 @@
+"""One Nsight Compute diagnostic round over a list of kernel variants and sizes.
+
+Counterpart of the reference's benchmarks/run_ncu_round.sh:40-81: for every "variant:size"
+pair, profile one settled launch of that kernel with a curated set of sections and keep the
+report, a readable detail page and a record of the commit, toolkit and driver.
+
+    python cuda-kernel-library_b200/ncu_round.py <round_name> <variant:size> [variant:size ...]
+    e.g.  ncu_round.py wide_vs_pair umma_2cta_wide:8192 umma_2cta:8192 umma_1cta:4096
+
+Output: <out>/<round_name>/<variant>_<size>.ncu-rep, the matching .txt (details page) and
+round_meta.txt; <out> defaults to ./ncu_rounds (--out to change).
+
+Differences from the reference script, all deliberate:
+  * every ncu call carries --clock-control none, so the GPU's clocks are never locked;
+  * each configuration is first run once WITHOUT ncu and is only profiled if that run exits 0;
+  * the kernel filter is this library's one tensor-core kernel (umma_gemm_kernel) or, for the
+    variant "sgemm", the FP32 kernel (sgemm_kernel);
+  * one launch is captured after two warm ones, with the same curated sections as the
+    reference (SpeedOfLight, Occupancy, MemoryWorkloadAnalysis, WarpStateStats,
+    SchedulerStats, LaunchStats, ComputeWorkloadAnalysis): a handful of passes, not --set full.
+Times printed by a run under ncu are not benchmark figures.
+"""
+
+from __future__ import annotations
+
+import argparse
+import datetime
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+DRIVER = os.path.join(HERE, "ncu_driver.py")
+SECTIONS = ["SpeedOfLight", "Occupancy", "MemoryWorkloadAnalysis", "WarpStateStats",
+            "SchedulerStats", "LaunchStats", "ComputeWorkloadAnalysis"]
+
+
+def tool_output(cmd: list[str]) -> str:
+    try:
+        return subprocess.run(cmd, capture_output=True, text=True, check=True).stdout.strip()
+    except Exception:
+        return "unknown"
+
+
+def driver_command(variant: str, size: int, dtype: str, beta: float) -> list[str]:
+    return [sys.executable, DRIVER, "--m", str(size), "--n", str(size), "--k", str(size), "--in", dtype,
+            "--out", dtype, "--beta", str(beta), "--algo", variant, "--iters", "3"]
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("round")
+    ap.add_argument("pairs", nargs="+", metavar="variant:size")
+    ap.add_argument("--out", default="ncu_rounds")
+    ap.add_argument("--dtype", choices=["f16", "bf16"], default="bf16")
+    ap.add_argument("--beta", type=float, default=0.0)
+    ap.add_argument("--ncu", default="ncu")
+    args = ap.parse_args()
+
+    out_dir = os.path.join(args.out, args.round)
+    os.makedirs(out_dir, exist_ok=True)
+    with open(os.path.join(out_dir, "round_meta.txt"), "w") as f:
+        f.write(f"round: {args.round}\n")
+        f.write(f"date: {datetime.datetime.now().astimezone().isoformat(timespec='seconds')}\n")
+        f.write(f"commit: {tool_output(['git', '-C', ROOT, 'rev-parse', 'HEAD'])}\n")
+        nvcc = tool_output(["nvcc", "--version"]).splitlines()
+        f.write(f"nvcc: {nvcc[-1] if nvcc else 'unknown'}\n")
+        f.write("driver: " + tool_output(["nvidia-smi", "--query-gpu=driver_version",
+                                          "--format=csv,noheader"]) + "\n")
+
+    failures = 0
+    for pair in args.pairs:
+        variant, _, size_text = pair.partition(":")
+        size = int(size_text)
+        kernel = "sgemm_kernel" if variant == "sgemm" else "umma_gemm_kernel"
+        base = os.path.join(out_dir, f"{variant}_{size}")
+        cmd = driver_command(variant, size, args.dtype, args.beta)
+        print(f"profiling {variant} at {size} cubed (kernel {kernel})", flush=True)
+        plain = subprocess.run(cmd, capture_output=True, text=True)
+        if plain.returncode != 0:
+            print(f"  not profiled: the plain run exited {plain.returncode}\n{plain.stderr[-800:]}")
+            failures += 1
+            continue
+        ncu = [args.ncu, "--clock-control", "none"]
+        for section in SECTIONS:
+            ncu += ["--section", section]
+        ncu += ["--kernel-name", f"regex:{kernel}", "--launch-skip", "2", "--launch-count", "1",
+                "--force-overwrite", "--export", base, *cmd]
+        run = subprocess.run(ncu, capture_output=True, text=True)
+        if run.returncode != 0:
+            print(f"  ncu exited {run.returncode}\n{run.stdout[-800:]}{run.stderr[-800:]}")
+            failures += 1
+            continue
+        details = subprocess.run([args.ncu, "--import", base + ".ncu-rep", "--page", "details"],
+                                 capture_output=True, text=True)
+        with open(base + ".txt", "w") as f:
+            f.write(details.stdout)
+        print(f"  wrote {base}.ncu-rep and {base}.txt")
+    return 1 if failures else 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -46,3 +46,36 @@ def test_sweep_resumes_and_forces(tmp_path):
     assert (ran, skipped) == (total - 1, 0)
     header = open(tmp_path / "summary.csv").readline().strip().split(",")
     assert header[:7] == ["family", "variant", "dtype", "m", "n", "k", "gpus"]
+
+
+def test_ncu_round_commands(tmp_path, monkeypatch):
+    """The profiling round (counterpart of benchmarks/run_ncu_round.sh of the reference) on CPU,
+    with stand-ins for ncu and for the GEMM driver: every ncu call leaves the clocks alone, the
+    plain run comes first and a configuration whose plain run fails is not profiled."""
+    import stat
+    import sys
+    path = os.path.join(ROOT, "cuda-kernel-library_b200", "ncu_round.py")
+    spec = importlib.util.spec_from_file_location("ckl_b200_ncu_round", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+
+    log = tmp_path / "calls.log"
+    fake_ncu = tmp_path / "fake_ncu"
+    fake_ncu.write_text(f"#!/bin/sh\necho \"$@\" >> {log}\n"
+                        "case \"$1\" in --import) echo details page;; esac\nexit 0\n")
+    fake_ncu.chmod(fake_ncu.stat().st_mode | stat.S_IEXEC)
+    fake_driver = tmp_path / "driver.py"
+    fake_driver.write_text("import sys\nsys.exit(7 if 'umma_1cta' in sys.argv else 0)\n")
+    monkeypatch.setattr(mod, "DRIVER", str(fake_driver))
+    monkeypatch.setattr(sys, "argv", ["ncu_round.py", "r1", "umma_2cta_wide:8192", "umma_1cta:4096",
+                                      "sgemm:2048", "--out", str(tmp_path), "--ncu", str(fake_ncu)])
+    assert mod.main() == 1                       # one configuration failed its plain run
+    calls = log.read_text().splitlines()
+    profiled = [c for c in calls if "--export" in c]
+    assert len(profiled) == 2 and all("--clock-control none" in c for c in profiled)
+    assert "regex:umma_gemm_kernel" in profiled[0] and "--launch-skip 2 --launch-count 1" in profiled[0]
+    assert "regex:sgemm_kernel" in profiled[1]
+    assert not any("umma_1cta" in c for c in calls)
+    assert (tmp_path / "r1" / "umma_2cta_wide_8192.txt").read_text().strip() == "details page"
+    meta = (tmp_path / "r1" / "round_meta.txt").read_text()
+    assert "round: r1" in meta and "commit:" in meta
