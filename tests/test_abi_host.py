@@ -108,9 +108,20 @@ def test_dispatch_follows_the_reference_contract(ckl):
     p = ckl.plan_gemm(8192, 8192, 8192, algo=ckl.ALGO_UMMA_1CTA)
     assert (p.tile_m, p.tile_n, p.tile_k) == (128, 256, 64)
     assert (p.tiles_m, p.tiles_n, p.k_blocks, p.grid) == (64, 32, 128, 148)
-    # the skinny stream-K stress shape splits by default; forcing the split works anywhere
+    # the skinny stream-K stress shape splits by default: 16 pair tiles, each cut at the same k
+    # offsets over 4 of the 74 pairs; forcing the split works anywhere
     p = ckl.plan_gemm(1024, 1024, 32768)
-    assert p.algo == ckl.ALGO_UMMA_SK and p.sk_tiles == 32 and p.workspace_bytes > 0
+    assert p.algo == ckl.ALGO_UMMA_2CTA_SK and p.sk_tiles == 16 and p.workspace_bytes > 0
+    assert p.units == 64 and p.dp_tiles == 0
+    assert [ckl.plan_sk_range(p, u)[0] % p.k_blocks for u in range(8)] == [0, 64, 128, 192] * 2
+    # with a short k per unit the single-CTA tiles keep the job (32 tiles x 4 CTAs)
+    p = ckl.plan_gemm(1024, 1024, 8192)
+    assert p.algo == ckl.ALGO_UMMA_SK and p.units == 128
+    # a thin last wave is split too, behind whole tiles (34 tiles left for 74 pairs)
+    p = ckl.plan_gemm(4096, 4096, 4096)
+    assert p.algo == ckl.ALGO_UMMA_2CTA_SK and (p.dp_tiles, p.sk_tiles, p.units) == (222, 34, 74)
+    # a nearly full last wave is not
+    assert ckl.plan_gemm(3072, 3072, 3072).sk_tiles == 0
     for algo in (ckl.ALGO_UMMA_SK, ckl.ALGO_UMMA_2CTA_SK, ckl.ALGO_UMMA_2CTA_WIDE_SK):
         p = ckl.plan_gemm(4000, 3000, 5000, algo=algo)
         assert p.sk_tiles > 0 and p.workspace_bytes > 0
