@@ -650,7 +650,15 @@ int gemm_impl(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, 
         // Fused where every unit has whole tiles left after its stream-K range, so the
         // reduction hides behind them; a launch that is all stream-K ends with the reduction
         // either way, and there the fix-up pass, spread over the whole GPU, measured faster.
-        if (!two_pass && plan.sched.dp_tiles >= plan.sched.units) {
+        // Not while the stream is being captured: a replayed graph would carry the same epoch
+        // every time, and the flags of the previous replay would pass for this one's.
+        cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &capture) != cudaSuccess) {
+            (void)cudaGetLastError();
+            capture = cudaStreamCaptureStatusActive;  // unknown: take the form that needs no epoch
+        }
+        if (!two_pass && plan.sched.dp_tiles >= plan.sched.units &&
+            capture == cudaStreamCaptureStatusNone) {
             p.sk_flags = flags;
             p.sk_epoch = epoch;
         }

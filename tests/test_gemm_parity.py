@@ -462,3 +462,37 @@ def test_reference_fusion_study_runs_unchanged(env):
     out = subprocess.run([exe], capture_output=True, text=True, timeout=300)
     print(out.stdout[-4000:])
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+
+
+def test_split_schedule_survives_graph_replay(env):
+    """A launch whose last wave is split, captured into a CUDA graph and replayed: every replay
+    must give what the same sequence of direct calls gives (C feeds back through beta, so a
+    replay that consumed stale partial tiles would show)."""
+    ckl = env.ckl
+    m, n, k = 2048, 2816, 2048          # 176 single-CTA tiles: one whole wave + 28 split tiles
+    plan = ckl.plan_gemm(m, n, k, algo=ckl.ALGO_UMMA_SK)
+    assert plan.sk_tiles > 0 and plan.dp_tiles >= plan.units
+    g = torch.Generator(device="cuda").manual_seed(5)
+    a = (torch.randn(m, k, device="cuda", generator=g) * 0.05).bfloat16()
+    b = (torch.randn(k, n, device="cuda", generator=g) * 0.05).bfloat16()
+    c0 = torch.randn(m, n, device="cuda", generator=g)
+    want = c0.clone()
+    for _ in range(3):
+        ckl.gemm_ex(ckl.BF16, a, b, want, ckl.F32, m, n, k, k, n, n, 1.0, 0.25, ckl.ALGO_UMMA_SK)
+    torch.cuda.synchronize()
+
+    stream = torch.cuda.Stream()
+    got = c0.clone()
+    scratch = c0.clone()
+    with torch.cuda.stream(stream):     # first call on this stream allocates its workspace
+        ckl.gemm_ex(ckl.BF16, a, b, scratch, ckl.F32, m, n, k, k, n, n, 1.0, 0.25, ckl.ALGO_UMMA_SK,
+                    stream.cuda_stream)
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        ckl.gemm_ex(ckl.BF16, a, b, got, ckl.F32, m, n, k, k, n, n, 1.0, 0.25, ckl.ALGO_UMMA_SK,
+                    stream.cuda_stream)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
