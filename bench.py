@@ -350,6 +350,7 @@ def run_ours(args) -> None:
 
     # ---- comparator on the same box: cuBLAS through torch.matmul (not the product) ------------
     cublas_tflops = None
+    cublas_beta_tflops = None
     if rank == 0:
         ref_b = b if world == 1 else torch.empty(K, N, dtype=torch.bfloat16, device="cuda").normal_()
         for _ in range(3):
@@ -362,6 +363,18 @@ def run_ours(args) -> None:
         r1.record()
         torch.cuda.synchronize()
         cublas_tflops = 2.0 * M * N * K / (r0.elapsed_time(r1) / args.steps * 1e-3) / 1e12
+        # the same workload (beta 0.5, C read and written in place) through cuBLAS
+        c_ref = torch.empty(M, N, dtype=torch.bfloat16, device="cuda").normal_(std=0.02)
+        for _ in range(3):
+            torch.addmm(c_ref, a, ref_b, beta=BETA, alpha=ALPHA, out=c_ref)
+        torch.cuda.synchronize()
+        r0.record()
+        for _ in range(args.steps):
+            torch.addmm(c_ref, a, ref_b, beta=BETA, alpha=ALPHA, out=c_ref)
+        r1.record()
+        torch.cuda.synchronize()
+        cublas_beta_tflops = 2.0 * M * N * K / (r0.elapsed_time(r1) / args.steps * 1e-3) / 1e12
+        del c_ref
 
     if rank == 0:
         peaks, peak_src = measured_peaks()
@@ -391,6 +404,7 @@ def run_ours(args) -> None:
             "gpu_launches": args.steps * launches_per_step * world,
             "clocks": clocks,
             "cublas_same_box_tflops": cublas_tflops,
+            "cublas_same_box_same_workload_tflops": cublas_beta_tflops,
         }
         if gathered is not None:
             line["gathered"] = gathered

@@ -287,12 +287,12 @@ int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_al
             static_cast<long long>((m + 255) / 256) * static_cast<long long>((n + 511) / 512);
         // The wide tile saves a quarter of the L2-to-SM traffic (higher clocks under the power
         // cap) but exposes its epilogue between tiles; measured, it wins only when the
-        // main loop is long (k >= 8192) and no tile column is mostly padding.
+        // main loop is long (k >= 4096) and no tile column is mostly padding.
         auto wave_fill = [&](long long tiles) {  // share of unit-slots the last wave leaves busy
             const long long waves = (tiles + max_pairs - 1) / max_pairs;
             return static_cast<double>(tiles) / static_cast<double>(waves * max_pairs);
         };
-        const bool use_wide = max_pairs > 0 && wide_tiles * 5 >= max_pairs * 4LL && k >= 8192 &&
+        const bool use_wide = max_pairs > 0 && wide_tiles * 5 >= max_pairs * 4LL && k >= 4096 &&
                               (n % 512 == 0 || n % 512 > 384) &&
                               wave_fill(wide_tiles) >= wave_fill(pair_tiles) - 0.02;
         // Fewer 256x256 tiles than half the pairs: split every tile over a whole number of
@@ -438,7 +438,7 @@ int launch_umma(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
     cfg.blockDim = dim3(Cfg::kThreads);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attrs[2];
+    cudaLaunchAttribute attrs[3];
     unsigned num_attrs = 0;
     if (Cfg::kPair) {
         attrs[num_attrs].id = cudaLaunchAttributeClusterDimension;
@@ -455,17 +455,29 @@ int launch_umma(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
         // that, fall through to the two-kernel form, where nobody waits for anybody.
         attrs[num_attrs].id = cudaLaunchAttributeCooperative;
         attrs[num_attrs].val.cooperative = 1;
-        cfg.numAttrs = num_attrs + 1;
-        if (cudaLaunchKernelEx(&cfg, umma_gemm_kernel<kMode, OutT>, ta, tb, tc, p) == cudaSuccess) {
-            return CKL_OK;
+        attrs[num_attrs + 1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[num_attrs + 1].val.programmaticStreamSerializationAllowed = 1;
+        // with the head start of a programmatic dependent if the driver takes both, else without
+        for (unsigned extra = 2; extra >= 1; --extra) {
+            cfg.numAttrs = num_attrs + extra;
+            if (cudaLaunchKernelEx(&cfg, umma_gemm_kernel<kMode, OutT>, ta, tb, tc, p) == cudaSuccess) {
+                return CKL_OK;
+            }
+            (void)cudaGetLastError();
         }
-        (void)cudaGetLastError();
         cfg.numAttrs = num_attrs;
     }
     GemmParams q = p;
     q.sk_flags = nullptr;
+    // Programmatic dependent launch: the prologue (barriers, tensor memory) may overlap the
+    // tail of the previous kernel in the stream; the kernel waits for that kernel before it
+    // touches global memory.  Ordinary stream order for anything that is not such a kernel.
+    attrs[num_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[num_attrs].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = num_attrs + 1;
     CKL_TRY_CUDA(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<kMode, OutT>, ta, tb, tc, q));
     if (q.sched.sk_tiles > 0) {
+        // ordinary launch: as a programmatic dependent it measured slower (1024x1024x32768)
         streamk_fixup_kernel<Cfg::kTileM, Cfg::kTileN, OutT>
             <<<dim3(static_cast<unsigned>(q.sched.sk_tiles), Cfg::kTileM / 32 * Cfg::kNHalves), 256, 0,
                stream>>>(q);

@@ -488,6 +488,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_ptr;
 
+    // Back-to-back launches: everything above touched only this CTA's shared and tensor
+    // memory, so it may run while the previous kernel of the stream is still finishing (the
+    // host launches this kernel as a programmatic dependent).  From here on global memory is
+    // read and written: wait for the previous kernel.  The kernel after this one gets the same
+    // head start: it needs an SM of its own anyway, so it can be let in right away.
+    ptx::grid_dependency_wait();
+    ptx::launch_dependents();
+
     const Schedule& sched = p.sched;
 #ifdef CKL_TIMERS
     const long long prof_c0 = clock64();

@@ -45,6 +45,17 @@ __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 
+// Programmatic dependent launch.  launch_dependents: the next kernel of the stream, if it was
+// launched as a programmatic dependent, may be scheduled once every CTA of this grid has said
+// so (or exited).  grid_dependency_wait: returns when the kernels this one depends on have
+// completed and their memory is visible; a no-op for an ordinary launch.
+__device__ __forceinline__ void launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // Flag words in global memory that one CTA publishes and another polls.
 __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
     unsigned int v;

@@ -118,8 +118,10 @@ def test_dispatch_follows_the_reference_contract(ckl):
     p = ckl.plan_gemm(1024, 1024, 8192)
     assert p.algo == ckl.ALGO_UMMA_SK and p.units == 128
     # a thin last wave is split too, behind whole tiles (34 tiles left for 74 pairs)
-    p = ckl.plan_gemm(4096, 4096, 4096)
+    p = ckl.plan_gemm(4096, 4096, 2048)
     assert p.algo == ckl.ALGO_UMMA_2CTA_SK and (p.dp_tiles, p.sk_tiles, p.units) == (222, 34, 74)
+    # from k = 4096 on the 256x512 tile takes over where its waves fill as well
+    assert ckl.plan_gemm(4096, 4096, 4096).algo == ckl.ALGO_UMMA_2CTA_WIDE
     # a nearly full last wave is not
     assert ckl.plan_gemm(3072, 3072, 3072).sk_tiles == 0
     for algo in (ckl.ALGO_UMMA_SK, ckl.ALGO_UMMA_2CTA_SK, ckl.ALGO_UMMA_2CTA_WIDE_SK):
