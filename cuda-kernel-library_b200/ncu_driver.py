@@ -4,7 +4,7 @@ Counterpart of the reference's benchmarks/ncu_driver.cpp:41-97 (run one variant 
 let `ncu --launch-skip` pick a warm launch).  Example, the capture behind the summaries in
 profiles/:
 
-    ncu --set full --clock-control none -k regex:umma_gemm_kernel -s 2 -c 1 -o gpurun_out/prof \
+    ncu --set full --clock-control none -k regex:umma_gemm_kernel -s 2 -c 1 -o prof \
         python cuda-kernel-library_b200/ncu_driver.py --m 8192 --n 8192 --k 8192 \
         --in bf16 --out bf16 --beta 0.5 --algo umma_1cta --iters 4
 

@@ -8,7 +8,7 @@ one configuration cannot take the sweep down); its JSON row is appended to `swee
 (family, variant, dtype, m, n, k, gpus, commit) is already in the file is skipped unless
 `--force` is given, so an interrupted sweep continues where it stopped.
 
-    python cuda-kernel-library_b200/sweep.py --out gpurun_out/sweep [--quick] [--force]
+    python cuda-kernel-library_b200/sweep.py --out sweep_results [--quick] [--force]
 
 The matrix holds the reference's square sizes and the benchmark configurations of this
 library's headline path (4096^3, 8192^3, the two stream-K stress shapes, one tensor-parallel
@@ -128,7 +128,7 @@ def sweep(out_dir: str, quick: bool = False, force: bool = False, commit: str | 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "sweep"))
+    ap.add_argument("--out", default=os.path.join(ROOT, "sweep_results"))
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--force", action="store_true")
     args = ap.parse_args()

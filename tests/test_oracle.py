@@ -38,7 +38,7 @@ def test_random_matrix_matches_reference(orc, entry):
         assert x.min() >= -1.0 and x.max() < 1.0
 
 
-def test_random_matrix_survey_known_answers(orc):
+def test_random_matrix_known_answers(orc):
     a = orc.random_matrix(512, 512, 0x1111 + 512)
     b = orc.random_matrix(512, 512, 0x2222 + 512)
     assert a.ravel()[0] == np.float32(-0.767540812)
