@@ -53,6 +53,23 @@ def test_fp32_ladder_is_mirrored_and_validates(ckl):
     assert e.value.status == ckl.ERR_INVALID_ARG
 
 
+def test_trsm_is_mirrored_and_validates(ckl):
+    # include/ckl/trsm.hpp:19-24 of the reference: trsm_naive, trsm_blocked (+ the cuBLAS oracle)
+    header = open(os.path.join(ROOT, "include", "ckl", "trsm.hpp")).read()
+    for name in ("trsm_naive", "trsm_blocked", "trsm_cublas"):
+        assert re.search(rf"\b{name}\s*\(", header), name
+    for name in ("trsm_naive", "trsm_blocked"):
+        assert callable(getattr(ckl, name))
+    ckl.trsm_blocked(None, None, 0, 8, 1.5)          # zero m or n: no-op, as the reference
+    ckl.trsm_naive(None, None, 8, 0, 1.5)
+    with pytest.raises(ckl.CklError) as e:
+        ckl.strsm_lower(None, 16, 4, 4)               # L null
+    assert e.value.status == ckl.ERR_INVALID_ARG
+    with pytest.raises(ckl.CklError) as e:
+        ckl.strsm_lower(16, 16, 8, 4, 4, 4)           # lda < m
+    assert e.value.status == ckl.ERR_INVALID_ARG
+
+
 def test_argument_validation_needs_no_gpu(ckl):
     # bad dtypes / algo / leading dimension are rejected before any CUDA call
     with pytest.raises(ckl.CklError) as e:
