@@ -220,7 +220,11 @@ Schedule make_schedule(int m, int n, int k, int mode, int max_units, int want_sk
     s.tiles_m = (m + d.tile_m - 1) / d.tile_m;
     s.tiles_n = (n + d.tile_n - 1) / d.tile_n;
     s.k_blocks = (k + d.tile_k - 1) / d.tile_k;
-    s.group_m = mode == kModeSingle ? 16 : 8;
+    // Raster group height: a wave of tiles should cover a block of C that is about as tall as
+    // it is wide, so that it reads the least A + B.  256x512 tiles are twice as wide as tall,
+    // so their groups are twice as high when there are columns enough (measured, 8192^3:
+    // 1599 vs 1592 TFLOP/s; 6144^3: 1550 vs 1538).
+    s.group_m = mode == kModeSingle ? 16 : (mode == kModePairWide && s.tiles_n >= 8) ? 16 : 8;
     const int tiles = s.tiles_m * s.tiles_n;
     s.units = std::max(1, std::min(max_units, tiles));
     s.dp_tiles = tiles;
