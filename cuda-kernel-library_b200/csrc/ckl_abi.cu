@@ -442,7 +442,7 @@ int launch_umma(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
     cfg.blockDim = dim3(Cfg::kThreads);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attrs[3];
+    cudaLaunchAttribute attrs[2];
     unsigned num_attrs = 0;
     if (Cfg::kPair) {
         attrs[num_attrs].id = cudaLaunchAttributeClusterDimension;
@@ -459,16 +459,11 @@ int launch_umma(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
         // that, fall through to the two-kernel form, where nobody waits for anybody.
         attrs[num_attrs].id = cudaLaunchAttributeCooperative;
         attrs[num_attrs].val.cooperative = 1;
-        attrs[num_attrs + 1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attrs[num_attrs + 1].val.programmaticStreamSerializationAllowed = 1;
-        // with the head start of a programmatic dependent if the driver takes both, else without
-        for (unsigned extra = 2; extra >= 1; --extra) {
-            cfg.numAttrs = num_attrs + extra;
-            if (cudaLaunchKernelEx(&cfg, umma_gemm_kernel<kMode, OutT>, ta, tb, tc, p) == cudaSuccess) {
-                return CKL_OK;
-            }
-            (void)cudaGetLastError();
+        cfg.numAttrs = num_attrs + 1;
+        if (cudaLaunchKernelEx(&cfg, umma_gemm_kernel<kMode, OutT>, ta, tb, tc, p) == cudaSuccess) {
+            return CKL_OK;
         }
+        (void)cudaGetLastError();
         cfg.numAttrs = num_attrs;
     }
     GemmParams q = p;
