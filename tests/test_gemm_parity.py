@@ -496,3 +496,41 @@ def test_split_schedule_survives_graph_replay(env):
         graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(got, want)
+
+
+_FORMS_SCRIPT = r"""
+import hashlib, importlib.util, os, sys
+import torch
+root = sys.argv[1]
+spec = importlib.util.spec_from_file_location("ckl_b200", os.path.join(root, "cuda-kernel-library_b200", "__init__.py"))
+ckl = importlib.util.module_from_spec(spec); spec.loader.exec_module(ckl)
+g = torch.Generator(device="cuda").manual_seed(9)
+for algo, (m, n, k) in [(ckl.ALGO_UMMA_SK, (2048, 2816, 2048)), (ckl.ALGO_UMMA_2CTA_SK, (4000, 3000, 5000)),
+                        (ckl.ALGO_UMMA_2CTA_WIDE_SK, (4000, 3000, 5000))]:
+    plan = ckl.plan_gemm(m, n, k, algo=algo)
+    assert plan.sk_tiles > 0 and plan.dp_tiles >= plan.units, (algo, plan.dp_tiles, plan.sk_tiles)
+    a = (torch.randn(m, k, device="cuda", generator=g) * 0.05).half()
+    b = (torch.randn(k, n, device="cuda", generator=g) * 0.05).half()
+    c = torch.randn(m, n, device="cuda", generator=g).half()
+    for _ in range(2):
+        ckl.gemm_ex(ckl.F16, a, b, c, ckl.F16, m, n, k, k, n, n, 1.0, 0.5, algo)
+    torch.cuda.synchronize()
+    ckl.device_status()
+    print(algo, hashlib.sha256(c.cpu().numpy().tobytes()).hexdigest())
+"""
+
+
+def test_fused_and_two_kernel_split_give_the_same_bits(env):
+    """Split schedules with whole tiles behind them, all three tile shapes: the fused form (the
+    holder of a tile's first k blocks adds the parked partials) and the two-kernel form
+    (CKL_STREAMK_FIXUP=pass) must agree bit for bit.  The form is chosen once per process, so
+    each runs in its own."""
+    import sys
+    outs = []
+    for form in ("", "pass"):
+        child_env = dict(os.environ, CKL_STREAMK_FIXUP=form)
+        run = subprocess.run([sys.executable, "-c", _FORMS_SCRIPT, ROOT], capture_output=True, text=True,
+                             timeout=600, env=child_env)
+        assert run.returncode == 0, run.stdout[-2000:] + run.stderr[-2000:]
+        outs.append(run.stdout.strip().splitlines())
+    assert len(outs[0]) == 3 and outs[0] == outs[1]
