@@ -111,7 +111,7 @@ Result run_fp32(int m, int n, int k, const std::string& root) {
 // L X = alpha B with the diagonally dominant L of the reference's TRSM test
 // (tests/test_trsm.cpp:20-31); m*m*n flops.  B is restored before every timed solve by a
 // device copy inside the timed lambda (the solve is in place), as the reference's row does.
-Result run_trsm(int m, int n) {
+Result run_trsm(int m, int n, const std::string& root) {
     Result r;
     auto hl = ckl::random_matrix(m, m, 11);
     for (int i = 0; i < m; ++i) {
@@ -140,6 +140,13 @@ Result run_trsm(int m, int n) {
     r.median_ms = ks.median_ms;
     r.iqr_ms = ks.iqr_ms;
     r.gflops = static_cast<double>(m) * m * n / (ks.median_ms * 1.0e6);
+    if (auto strsm = ckl_tools::find_trsm_comparator(root)) {
+        const ckl::TimingStats os = ckl::time_stream([&](cudaStream_t s) {
+            cudaMemcpyAsync(db.data(), db0.data(), hb.size() * sizeof(float), cudaMemcpyDeviceToDevice, s);
+            strsm(dl.data(), db.data(), m, n, 1.0f, s);
+        });
+        r.baseline_gflops = static_cast<double>(m) * m * n / (os.median_ms * 1.0e6);
+    }
     return r;
 }
 
@@ -171,7 +178,7 @@ int main(int argc, char** argv) {
     monitor.start();
     Result r;
     try {
-        r = family == "trsm" ? run_trsm(m, n)
+        r = family == "trsm" ? run_trsm(m, n, root)
             : fp32           ? run_fp32(m, n, k, root)
             : bf16           ? run<__nv_bfloat16>(algo, c16, true, m, n, k, root)
                              : run<__half>(algo, c16, false, m, n, k, root);

@@ -164,4 +164,15 @@ inline CublasFn32 find_sgemm_comparator(const std::string& repo_root) {
     return reinterpret_cast<CublasFn32>(dlsym(lib, "_ZN3ckl11gemm_cublasEPKfS1_PfiiiffP11CUstream_st"));
 }
 
+// The reference's STRSM wrapper (ckl::trsm_cublas, src/trsm/cublas_trsm.cpp), same lookup.
+using CublasTrsmFn = void (*)(const float*, float*, int, int, float, cudaStream_t);
+inline CublasTrsmFn find_trsm_comparator(const std::string& repo_root) {
+    const std::string path = repo_root + "/oracle/_ref/libckl_ref_gemm.so";
+    void* lib = dlopen(path.c_str(), RTLD_NOW | RTLD_LOCAL);
+    if (lib == nullptr) {
+        return nullptr;
+    }
+    return reinterpret_cast<CublasTrsmFn>(dlsym(lib, "_ZN3ckl11trsm_cublasEPKfPfiifP11CUstream_st"));
+}
+
 }  // namespace ckl_tools
