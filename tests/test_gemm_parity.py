@@ -368,6 +368,11 @@ def test_config_mlp_shard(env):
     _run_large(env, 16384, 1792, 4096, env.ckl.BF16, env.ckl.BF16, 1.0, 0.0, "mlp", 6, 4)
 
 
+def test_config_mlp_whole(env):
+    # the same MLP-shaped problem unsharded on one GPU: M=16384, K=4096, N=14336
+    _run_large(env, 16384, 14336, 4096, env.ckl.BF16, env.ckl.BF16, 1.0, 0.0, "mlp", 4, 4)
+
+
 # ---------------------------------------------------------------------------------------
 # neighbours of the path: fused epilogue, host-buffer call, column-block assembly
 # ---------------------------------------------------------------------------------------
