@@ -458,7 +458,8 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--algo", default="auto",
                     help="pin a kernel (auto, simt, umma_1cta, umma_1cta_streamk, umma_2cta, "
-                         "umma_2cta_streamk); the default is what every caller gets")
+                         "umma_2cta_streamk, umma_2cta_wide, umma_2cta_wide_streamk); the default "
+                         "is what every caller gets")
     args = ap.parse_args()
     if args.gpus <= 1 or "WORLD_SIZE" in os.environ:
         keep_stdout_for_the_result()   # (the torchrun re-launch below passes its child's stdout through)
