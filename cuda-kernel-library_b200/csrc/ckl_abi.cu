@@ -277,8 +277,10 @@ Schedule make_schedule(int m, int n, int k, int mode, int max_units, int want_sk
     return s;
 }
 
+// c_traffic: bytes of C moved per output element by the epilogue (element size, doubled when
+// C is also read), which sets how long the exposed epilogue of the 256x512 tile is.
 int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_align, int algo,
-              int sm_count, int max_pairs, Plan* plan) {
+              int sm_count, int max_pairs, int c_traffic, Plan* plan) {
     const bool legal = tma_legal(k, lda, ldb, a_align, b_align);
     int resolved = algo;
     if (algo == CKL_ALGO_AUTO) {
@@ -291,12 +293,15 @@ int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_al
             static_cast<long long>((m + 255) / 256) * static_cast<long long>((n + 511) / 512);
         // The wide tile saves a quarter of the L2-to-SM traffic (higher clocks under the power
         // cap) but exposes its epilogue between tiles; measured, it wins only when the
-        // main loop is long (k >= 4096) and no tile column is mostly padding.
+        // main loop is long (k >= 4096; 8192 when the epilogue both reads and writes an FP32
+        // C: 16384x14336x4096, FP32 C, beta 0.5: 1301 vs 1368 TFLOP/s on the 256x256 tile) and no
+        // tile column is mostly padding.
         auto wave_fill = [&](long long tiles) {  // share of unit-slots the last wave leaves busy
             const long long waves = (tiles + max_pairs - 1) / max_pairs;
             return static_cast<double>(tiles) / static_cast<double>(waves * max_pairs);
         };
-        const bool use_wide = max_pairs > 0 && wide_tiles * 5 >= max_pairs * 4LL && k >= 4096 &&
+        const int wide_min_k = c_traffic >= 8 ? 8192 : 4096;  // FP32 C read and written: longer drain
+        const bool use_wide = max_pairs > 0 && wide_tiles * 5 >= max_pairs * 4LL && k >= wide_min_k &&
                               (n % 512 == 0 || n % 512 > 384) &&
                               wave_fill(wide_tiles) >= wave_fill(pair_tiles) - 0.02;
         // Fewer 256x256 tiles than half the pairs: split every tile over a whole number of
@@ -579,8 +584,10 @@ int gemm_impl(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, 
     Plan plan;
     const size_t a_align = reinterpret_cast<uintptr_t>(a) % 16 == 0 ? 16 : 2;
     const size_t b_align = reinterpret_cast<uintptr_t>(b) % 16 == 0 ? 16 : 2;
+    const int c_traffic = static_cast<int>(dtype_size(c_dtype)) *
+                          ((epi == kEpiLinear && beta != 0.0f) ? 2 : 1);
     if (const int rc = make_plan(m, n, k, lda, ldb, a_align, b_align, algo, ctx->sm_count,
-                                 ctx->max_pairs, &plan);
+                                 ctx->max_pairs, c_traffic, &plan);
         rc != CKL_OK) {
         return rc;
     }
@@ -969,7 +976,8 @@ int ckl_plan_gemm(int m, int n, int k, int lda, int ldb, int ldc, int a_align, i
     }
     Plan plan;
     if (const int rc = make_plan(m, n, k, lda, ldb, static_cast<size_t>(a_align),
-                                 static_cast<size_t>(b_align), algo, sm_count, sm_count / 2, &plan);
+                                 static_cast<size_t>(b_align), algo, sm_count, sm_count / 2,
+                                 /*c_traffic=*/2, &plan);
         rc != CKL_OK) {
         return rc;
     }

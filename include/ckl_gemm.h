@@ -131,7 +131,9 @@ int ckl_gemm_host(int ab_dtype, const void* a_host, const void* b_host, void* c_
 /* Host-side planning, no GPU needed: what ckl_gemm_ex would launch for this
  * shape on a device with `sm_count` SMs.  Mirrors the role of the reference's
  * launch_wmma dispatch test (include/ckl/detail/wmma_gemm.cuh:148) as a pure
- * function so it can be unit-tested on a CPU. */
+ * function so it can be unit-tested on a CPU.  The plan is the one for a 16-bit
+ * C or beta == 0; with an FP32 C and beta != 0, CKL_ALGO_AUTO keeps the 256x256
+ * tile up to k = 8192 instead of 4096 (the only output-dependent choice). */
 typedef struct ckl_plan {
     int algo;           /* resolved ckl_algo */
     int tile_m, tile_n; /* output tile of one work unit (per CTA pair for 2-CTA) */
