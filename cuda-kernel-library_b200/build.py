@@ -54,22 +54,6 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
-TIMERS_LIB = os.path.join(HERE, "libckl_gemm_timers.so")
-
-
-def build_timers() -> str:
-    """The same sources with -DCKL_TIMERS: in-kernel cycle counters for kernel_timers.py.  Never
-    loaded by the package; measurements taken with it are not benchmark figures."""
-    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    cmd = [nvcc, *NVCC_FLAGS, "-DCKL_TIMERS", "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-o",
-           TIMERS_LIB, *sources()]
-    subprocess.run(cmd, check=True)
-    return TIMERS_LIB
-
-
 if __name__ == "__main__":
-    if "--timers" in sys.argv:
-        print(build_timers())
-    else:
-        build(force="--force" in sys.argv, verbose="-v" in sys.argv)
-        print(LIB)
+    build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    print(LIB)

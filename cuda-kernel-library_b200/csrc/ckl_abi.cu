@@ -32,9 +32,6 @@ namespace {
 using namespace ckl;
 
 thread_local std::string g_last_error;
-#ifdef CKL_TIMERS
-unsigned long long* g_timer_buf = nullptr;  // instrumented builds: counters of the last launch
-#endif
 
 int fail(int code, const char* fmt, ...) {
     char buf[512];
@@ -642,17 +639,6 @@ int gemm_impl(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, 
     p.idesc = ptx::make_idesc_f16(ab_dtype == CKL_F16 ? 0u : 1u, 0u, 1u, plan.pair ? 256u : 128u,
                                   256u);
     p.sched = plan.sched;
-#ifdef CKL_TIMERS
-    {
-        const char* mode = std::getenv("CKL_TIMER_MODE");
-        p.timer_mode = mode != nullptr ? std::atoi(mode) : 0;
-        if (g_timer_buf == nullptr) {
-            cudaMalloc(&g_timer_buf, 1024 * 8 * sizeof(unsigned long long));
-        }
-        cudaMemsetAsync(g_timer_buf, 0, 1024 * 8 * sizeof(unsigned long long), stream);
-        p.timers = g_timer_buf;
-    }
-#endif
     if (plan.workspace_bytes > 0) {
         unsigned int* flags = nullptr;
         unsigned int epoch = 0;
@@ -1139,16 +1125,6 @@ int ckl_stream_copy(void* dst, const void* src, size_t bytes, ckl_stream_t strea
     return CKL_OK;
 }
 
-#ifdef CKL_TIMERS
-// Instrumented builds only: waits for the device and copies the counters of the last launch
-// (eight per CTA) to `out`.
-int ckl_read_timers(unsigned long long* out, int ctas) {
-    cudaDeviceSynchronize();
-    return g_timer_buf ? static_cast<int>(cudaMemcpy(out, g_timer_buf, sizeof(unsigned long long) * 8 * ctas,
-                                                     cudaMemcpyDeviceToHost))
-                       : -1;
-}
-#endif
 
 const char* ckl_last_error(void) { return g_last_error.c_str(); }
 

@@ -67,12 +67,6 @@ struct GemmParams {
     int epi_mode;
     uint32_t idesc;
     Schedule sched;
-#ifdef CKL_TIMERS
-    // Instrumented builds only (-DCKL_TIMERS, see kernel_timers.py): eight counters per CTA.
-    // timer_mode 0: cycles per epilogue phase; 1: wall-clock timeline of a stream-K launch.
-    int timer_mode;
-    unsigned long long* timers;
-#endif
 };
 
 // Depth of the shared-memory ring (48 KB per stage for one CTA, 64 KB per CTA of a pair).
@@ -405,9 +399,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     constexpr bool kPair = Cfg::kPair;
     constexpr bool kWide = Cfg::kWide;
     constexpr int kStages = Cfg::kStages;
-#ifdef CKL_TIMERS
-    const unsigned long long prof_entry = ptx::global_timer_ns();
-#endif
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -497,16 +488,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ptx::launch_dependents();
 
     const Schedule& sched = p.sched;
-#ifdef CKL_TIMERS
-    const long long prof_c0 = clock64();
-    const unsigned long long prof_t0 = ptx::global_timer_ns();
-    long long prof_wait = 0, prof_wait2 = 0;
-#define CKL_PROF_BEGIN() const long long prof_b_ = clock64()
-#define CKL_PROF_END(acc_) acc_ += clock64() - prof_b_
-#else
-#define CKL_PROF_BEGIN()
-#define CKL_PROF_END(acc_)
-#endif
 
     // ---- roles ----------------------------------------------------------------
     if (warp == 0) {
@@ -526,10 +507,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 const int b_col = tn * Cfg::kTileN + (kPair ? static_cast<int>(rank) * 128 : 0);
                 for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb) {
                     {
-                        CKL_PROF_BEGIN();
                         const bool got = detail::wait_barrier(empty_bar(stage), phase ^ 1u, ctl,
                                                               kRoleProducer, it);
-                        CKL_PROF_END(prof_wait);
                         if (!got) {
                             ok = false;
                             break;
@@ -635,19 +614,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t phase = 0;
             uint32_t seg_count = 0;
             bool ok = true;
-#ifdef CKL_TIMERS
-            unsigned long long tl_sk_start = 0;
-#endif
             while (ok && next_segment(sched, &cur, &seg)) {
-#ifdef CKL_TIMERS
-                if (tl_sk_start == 0 && seg.tile >= sched.dp_tiles) tl_sk_start = ptx::global_timer_ns();
-#endif
                 // Two accumulators, used alternately (kAccStages == 2), or one accumulator
                 // of two 256-column halves that the epilogue hands back one by one.
                 const uint32_t acc = kWide ? 0u : (seg_count & 1u);
                 const uint32_t acc_parity = kWide ? (seg_count & 1u) : ((seg_count >> 1) & 1u);
                 {
-                    CKL_PROF_BEGIN();
                     bool got = detail::wait_barrier(acc_empty_bar(static_cast<int>(acc)),
                                                     acc_parity ^ 1u, ctl, kRoleMma,
                                                     0x80000000u | seg_count);
@@ -655,7 +627,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         got = detail::wait_barrier(acc_empty_bar(1), acc_parity ^ 1u, ctl, kRoleMma,
                                                    0x90000000u | seg_count);
                     }
-                    CKL_PROF_END(prof_wait2);
                     if (!got) {
                         ok = false;
                         break;
@@ -669,9 +640,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 bool ready = false;
                 for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb) {
                     if (!ready) {
-                        CKL_PROF_BEGIN();
                         const bool got = detail::wait_barrier(full_bar(stage), phase, ctl, kRoleMma, it);
-                        CKL_PROF_END(prof_wait);
                         if (!got) {
                             ok = false;
                             break;
@@ -735,18 +704,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     ++seg_count;
                 }
             }
-#ifdef CKL_TIMERS
-            if (p.timers) {
-                p.timers[blockIdx.x * 8 + 0] = static_cast<unsigned long long>(clock64() - prof_c0);
-                p.timers[blockIdx.x * 8 + 5] = static_cast<unsigned long long>(prof_wait2);
-                p.timers[blockIdx.x * 8 + 6] = it;
-                if (p.timer_mode == 1) {
-                    p.timers[blockIdx.x * 8 + 1] = prof_entry;
-                    p.timers[blockIdx.x * 8 + 2] = tl_sk_start;
-                    p.timers[blockIdx.x * 8 + 3] = ptx::global_timer_ns();
-                }
-            }
-#endif
             if (ok) {
                 // Tail: the epilogue (of both CTAs) must have drained the last
                 // accumulators before TMEM can go.
@@ -798,12 +755,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const bool reads_c = (p.epi_mode == kEpiLinear) && (p.beta != 0.0f);
         const bool unit_alpha = p.alpha == 1.0f;
         bool alive = true;
-#ifdef CKL_TIMERS
-        long long ep_ld = 0, ep_cw = 0, ep_ci = 0, ep_cp = 0, ep_st = 0, ep_t = 0;
-#define CKL_EP(acc_) do { const long long n_ = clock64(); acc_ += n_ - ep_t; ep_t = n_; } while (0)
-#else
-#define CKL_EP(acc_) do { } while (0)
-#endif
         while (alive && next_segment(sched, &cur, &seg)) {
             const uint32_t acc = kWide ? 0u : (seg_count & 1u);
             const uint32_t acc_parity = kWide ? (seg_count & 1u) : ((seg_count >> 1) & 1u);
@@ -909,9 +860,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
             ptx::tc_fence_after_sync();
 
-#ifdef CKL_TIMERS
-            const unsigned long long tl_w0 = ptx::global_timer_ns();
-#endif
             if (peers > 0) {
                 // Wait (bounded) until every peer's warp of the same rows and columns has parked
                 // its partial.  Each lane then reads the flags itself, so that its loads of the
@@ -939,11 +887,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
             }
 
-#ifdef CKL_TIMERS
-            if (p.timer_mode == 1) {
-                ep_cw += static_cast<long long>(ptx::global_timer_ns() - tl_w0);
-            }
-#endif
             if (parks) {
                 // Partial accumulator -> FP32 workspace slot, whole tile, no predication.  The
                 // slot is not row-major: it is the image of the registers, laid out as
@@ -1010,7 +953,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         }
                         cin_parity ^= 1u << b;
                     }
-                    CKL_EP(ep_cw);
                     if (reads_c && c >= 1 && c + 1 < n_chunks && lane == 0) {
                         // Buffer b^1 was the source of the previous chunk's store; once that
                         // store has read it, the C_in of the next chunk can land there.
@@ -1020,7 +962,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                          col + kChunkCols, row0);
                         cin_pending |= 1u << (b ^ 1u);
                     }
-                    CKL_EP(ep_ci);
                     uint8_t* row_smem = stg_ptr + b * 4096u + lane * 128u;
                     // All eight 16-byte units of C_in are read before any result is written
                     // back: reads and writes share the buffer, and interleaving them would
@@ -1074,21 +1015,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     } else {
                         emit([&](int j, int e) { return p.alpha * acc_of(j, e); });
                     }
-                    CKL_EP(ep_cp);
                     ptx::fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
                         ptx::tma_store_2d(&tmap_c, stg + b * 4096u, col, row0);
                         ptx::bulk_commit_group();
                     }
-                    CKL_EP(ep_st);
                     return true;
                 };
 #pragma unroll 1
                 for (int c = 0; c < n_chunks && alive; ++c) {
-#ifdef CKL_TIMERS
-                    ep_t = clock64();
-#endif
                     uint32_t r[kChunkCols];
                     load_acc(c, r);
                     ptx::tmem_ld_wait();
@@ -1101,7 +1037,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             add_partials(c * (kChunkCols / 32) + h, r + h * 32);
                         }
                     }
-                    CKL_EP(ep_ld);
                     alive = finish_chunk(c, r);
                 }
                 if (!alive) {
@@ -1140,18 +1075,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             __syncwarp();
             ++seg_count;
         }
-#ifdef CKL_TIMERS
-        if (p.timers && ew == 0 && lane == 0 && (p.timer_mode == 1)) {
-            p.timers[blockIdx.x * 8 + 4] = ptx::global_timer_ns();
-            p.timers[blockIdx.x * 8 + 7] = static_cast<unsigned long long>(ep_cw);
-        } else if (p.timers && ew == 0 && lane == 0) {
-            p.timers[blockIdx.x * 8 + 1] = static_cast<unsigned long long>(ep_ld);
-            p.timers[blockIdx.x * 8 + 2] = static_cast<unsigned long long>(ep_cw);
-            p.timers[blockIdx.x * 8 + 3] = static_cast<unsigned long long>(ep_ci);
-            p.timers[blockIdx.x * 8 + 4] = static_cast<unsigned long long>(ep_cp);
-            p.timers[blockIdx.x * 8 + 7] = static_cast<unsigned long long>(ep_st);
-        }
-#endif
         if (lane == 0) {
             // Leaving: no store may still read staging, no C_in copy may still write it.
             ptx::bulk_wait_group_read<0>();

@@ -35,6 +35,13 @@ _u16p = ctypes.POINTER(ctypes.c_uint16)
 _ip = ctypes.POINTER(ctypes.c_int)
 
 
+def reference_tree() -> str:
+    """Where the reference library's source tree is looked for: $CKL_REFERENCE, else a
+    checkout named ``reference`` beside this repository.  It may be absent."""
+    return os.environ.get("CKL_REFERENCE") or os.path.join(
+        os.path.dirname(os.path.dirname(_HERE)), "reference")
+
+
 def build(force: bool = False) -> None:
     """Compile the plain-C oracle (and the reference shim where the reference
     tree is mounted).  Building the checker is not using it."""
@@ -42,7 +49,7 @@ def build(force: bool = False) -> None:
         os.path.join(_HERE, "ckl_oracle.c")
     ):
         subprocess.run(["make", "-s", "-C", _HERE, "oracle"], check=True)
-    reference = os.environ.get("CKL_REFERENCE", "/root/reference")
+    reference = reference_tree()
     if os.path.isdir(os.path.join(reference, "include", "ckl")):
         subprocess.run(["make", "-s", "-C", _HERE, "ref", f"REFERENCE={reference}"], check=True)
 

@@ -34,6 +34,45 @@ def load_package():
     return mod
 
 
+def reference_tree():
+    """The reference library's source tree, or None where it is not mounted."""
+    path = os.environ.get("CKL_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
+    return path if os.path.isdir(os.path.join(path, "include", "ckl")) else None
+
+
+def dropin_binary(name: str) -> str:
+    """Path of a reference driver built unchanged against this library (oracle/_ref/<name>).
+    Where the reference tree is mounted a missing binary is built, and a failure to build it
+    fails the test; only a machine with neither the tree nor a prebuilt binary skips."""
+    exe = os.path.join(ROOT, "oracle", "_ref", name)
+    if os.path.exists(exe):
+        return exe
+    ref = reference_tree()
+    if ref is None:
+        pytest.skip(f"oracle/_ref/{name} was not shipped and the reference tree is not mounted")
+    import subprocess
+    load_package()  # the drivers link libckl_gemm.so
+    out = subprocess.run(["make", "-s", "-C", os.path.join(ROOT, "oracle"), "dropin", f"REFERENCE={ref}"],
+                         capture_output=True, text=True)
+    if out.returncode != 0 or not os.path.exists(exe):
+        pytest.fail(f"could not build oracle/_ref/{name} from {ref}:\n{out.stderr[-2000:]}")
+    return exe
+
+
+def tool_binary(name: str) -> str:
+    """Path of a command-line tool of this library (cuda-kernel-library_b200/build/<name>);
+    built on demand, and a tool that cannot be built fails the test."""
+    exe = os.path.join(PKG_DIR, "build", name)
+    if os.path.exists(exe):
+        return exe
+    import subprocess
+    load_package()
+    out = subprocess.run(["make", "-s", "-C", os.path.join(PKG_DIR, "tools")], capture_output=True, text=True)
+    if out.returncode != 0 or not os.path.exists(exe):
+        pytest.fail(f"could not build {exe}:\n{out.stderr[-2000:]}")
+    return exe
+
+
 @pytest.fixture(scope="session")
 def ckl():
     return load_package()

@@ -19,6 +19,8 @@ import subprocess
 import numpy as np
 import pytest
 
+from conftest import dropin_binary
+
 torch = pytest.importorskip("torch")
 
 pytestmark = pytest.mark.gpu
@@ -449,21 +451,31 @@ def test_assemble_column_blocks(env):
 def test_reference_test_driver_runs_unchanged(env):
     """The reference's own tests/test_gemm_tensor.cpp, compiled without edits against this
     repository's include/ckl headers and library (oracle/Makefile target `dropin`), passes."""
-    exe = os.path.join(ROOT, "oracle", "_ref", "test_gemm_tensor_dropin")
-    if not os.path.exists(exe):
-        pytest.skip("oracle/_ref/test_gemm_tensor_dropin not built (needs the reference tree)")
+    exe = dropin_binary("test_gemm_tensor_dropin")
     out = subprocess.run([exe], capture_output=True, text=True, timeout=300)
     print(out.stdout[-4000:])
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
     assert "all tensor GEMM cases passed" in out.stdout
 
 
+def test_reference_bench_driver_runs_unchanged(env):
+    """The reference's benchmarks/bench_gemm_tensor.cpp, compiled without edits against this
+    repository's headers and library, runs its five entry points at 512^3 and prints one row
+    per entry point with a positive rate."""
+    exe = dropin_binary("bench_gemm_tensor_dropin")
+    out = subprocess.run([exe, "512"], capture_output=True, text=True, timeout=300)
+    print(out.stdout[-4000:])
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    rows = [ln.split() for ln in out.stdout.splitlines() if "gflops" in ln]
+    assert [r[0] for r in rows] == ["fp16", "bf16", "ptx", "ldm", "opt"]
+    for r in rows:
+        assert r[1] == "512" and float(r[3]) > 0.0
+
+
 def test_reference_fusion_study_runs_unchanged(env):
     """The reference's benchmarks/fusion_study.cpp (fused bias+ReLU epilogue against GEMM plus a
     separate pass), compiled without edits against this repository's headers and library."""
-    exe = os.path.join(ROOT, "oracle", "_ref", "fusion_study_dropin")
-    if not os.path.exists(exe):
-        pytest.skip("oracle/_ref/fusion_study_dropin not built (needs the reference tree)")
+    exe = dropin_binary("fusion_study_dropin")
     out = subprocess.run([exe], capture_output=True, text=True, timeout=300)
     print(out.stdout[-4000:])
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]

@@ -10,6 +10,8 @@ Shapes, alpha, beta and seeds are the reference's (tests/test_gemm.cpp:71-76,108
 import numpy as np
 import pytest
 
+from conftest import dropin_binary
+
 torch = pytest.importorskip("torch")
 
 pytestmark = pytest.mark.gpu
@@ -120,10 +122,22 @@ def test_reference_fp32_test_driver_runs_unchanged():
     import os
     import subprocess
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    exe = os.path.join(root, "oracle", "_ref", "test_gemm_dropin")
-    if not os.path.exists(exe):
-        pytest.skip("oracle/_ref/test_gemm_dropin not built (needs the reference tree)")
+    exe = dropin_binary("test_gemm_dropin")
     out = subprocess.run([exe], capture_output=True, text=True, timeout=300)
     print(out.stdout[-4000:])
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
     assert "all GEMM cases passed" in out.stdout
+
+
+def test_reference_fp32_bench_driver_runs_unchanged():
+    """The reference's benchmarks/bench_gemm.cpp, compiled without edits against this
+    repository's headers and library, times its four FP32 rungs and SGEMM at 256^3."""
+    import subprocess
+    exe = dropin_binary("bench_gemm_dropin")
+    out = subprocess.run([exe, "256"], capture_output=True, text=True, timeout=300)
+    print(out.stdout[-4000:])
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    rows = [ln.split() for ln in out.stdout.splitlines()[1:] if ln.strip()]
+    assert [r[1] for r in rows] == ["naive", "tiled", "register", "cp_async", "cublas"]
+    for r in rows:
+        assert r[0] == "256" and float(r[3]) > 0.0

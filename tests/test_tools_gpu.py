@@ -7,6 +7,8 @@ import subprocess
 
 import pytest
 
+from conftest import tool_binary
+
 pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -14,9 +16,7 @@ BUILD = os.path.join(ROOT, "cuda-kernel-library_b200", "build")
 
 
 def _run(args):
-    exe = os.path.join(BUILD, args[0])
-    if not os.path.exists(exe):
-        pytest.skip(f"{exe} not built (make -C cuda-kernel-library_b200/tools)")
+    exe = tool_binary(args[0])
     env = dict(os.environ, CKL_REPO_ROOT=ROOT)
     out = subprocess.run([exe, *args[1:]], capture_output=True, text=True, timeout=300, env=env)
     assert out.returncode == 0, out.stderr[-2000:]

@@ -11,6 +11,8 @@ leading-dimension cases.
 import numpy as np
 import pytest
 
+from conftest import dropin_binary
+
 torch = pytest.importorskip("torch")
 
 pytestmark = pytest.mark.gpu
@@ -98,9 +100,7 @@ def test_reference_trsm_test_driver_runs_unchanged():
     import os
     import subprocess
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    exe = os.path.join(root, "oracle", "_ref", "test_trsm_dropin")
-    if not os.path.exists(exe):
-        pytest.skip("oracle/_ref/test_trsm_dropin not built (needs the reference tree)")
+    exe = dropin_binary("test_trsm_dropin")
     out = subprocess.run([exe], capture_output=True, text=True, timeout=300)
     print(out.stdout[-4000:])
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
