@@ -273,6 +273,21 @@ def gemm_streamk_noalloc(ab_dtype, a, b, c, c_dtype, m, n, k, lda, ldb, ldc, alp
         raise CklError(status, _lib.ckl_noalloc_last_error().decode())
 
 
+_lib.ckl_noalloc_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
+_lib.ckl_noalloc_device_status.restype = ctypes.c_int
+
+
+def noalloc_device_status() -> list[int]:
+    """Health word of the allocation-free entry point (its kernels do not share the regular
+    entry points' word); synchronises, raises CklError(ERR_DEVICE) if a wait ran out.  Allocates
+    nothing."""
+    info = (ctypes.c_uint * 4)()
+    status = _lib.ckl_noalloc_device_status(info)
+    if status != OK:
+        raise CklError(status, _lib.ckl_noalloc_last_error().decode())
+    return list(info)
+
+
 def noalloc_scratch_bytes() -> int:
     return int(_lib.ckl_noalloc_scratch_bytes())
 

@@ -14,7 +14,11 @@
 //
 // What that costs.  Every GPU that loads the library carries the array
 // (kScratchBytes, 37 MiB) until the process exits, whether or not this entry
-// point is called.  The array is sized for a schedule of at most
+// point is called.  The CUDA runtime backs the array with device memory when it
+// loads this library's device code on a GPU, which with lazy module loading
+// happens at the first call made from this file on that GPU: a host that is
+// about to hand all device memory to its own arena must make that first call
+// BEFORE it does so, or the load itself runs out of memory.  The array is sized for a schedule of at most
 // kMaxUnits = 148 CTAs (a B200); a device whose schedule would need more is
 // refused with CKL_ERR_TOO_LARGE rather than run with a smaller grid.
 //
@@ -54,7 +58,7 @@ namespace {
 using namespace ckl;
 
 constexpr int kMaxUnits = 148;
-constexpr size_t kSlotBytes = UmmaConfig<false>::kSlotFloats * sizeof(float);  // 128 KB
+constexpr size_t kSlotBytes = UmmaConfig<kModeSingle>::kSlotFloats * sizeof(float);  // 128 KB
 constexpr size_t kScratchBytes = 2 * static_cast<size_t>(kMaxUnits) * kSlotBytes;  // 38,797,312
 
 // The scratch itself.  Device code could name these directly; host code below
@@ -99,9 +103,9 @@ int fail(int code, const char* fmt, ...) {
 
 template <typename OutT>
 cudaError_t raise_smem_limit() {
-    return cudaFuncSetAttribute(umma_gemm_kernel<false, OutT>,
+    return cudaFuncSetAttribute(umma_gemm_kernel<kModeSingle, OutT>,
                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                static_cast<int>(UmmaConfig<false>::kSmemBytes));
+                                static_cast<int>(UmmaConfig<kModeSingle>::kSmemBytes));
 }
 
 // One-time, per device, with that device current.  Allocates nothing.
@@ -166,11 +170,11 @@ int encode(const DeviceState& st, CUtensorMap* map, int dtype, const void* base,
 template <typename OutT>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
            int grid, cudaStream_t stream) {
-    umma_gemm_kernel<false, OutT>
-        <<<grid, UmmaConfig<false>::kThreads, UmmaConfig<false>::kSmemBytes, stream>>>(ta, tb, tc, p);
+    umma_gemm_kernel<kModeSingle, OutT>
+        <<<grid, UmmaConfig<kModeSingle>::kThreads, UmmaConfig<kModeSingle>::kSmemBytes, stream>>>(ta, tb, tc, p);
     NOALLOC_TRY(cudaGetLastError());
     if (p.sched.sk_tiles > 0) {
-        streamk_fixup_kernel<UmmaConfig<false>::kTileM, UmmaConfig<false>::kTileN, OutT><<<dim3(static_cast<unsigned>(p.sched.sk_tiles), UmmaConfig<false>::kTileM / 32), 256, 0, stream>>>(p);
+        streamk_fixup_kernel<UmmaConfig<kModeSingle>::kTileM, UmmaConfig<kModeSingle>::kTileN, OutT><<<dim3(static_cast<unsigned>(p.sched.sk_tiles), UmmaConfig<kModeSingle>::kTileM / 32), 256, 0, stream>>>(p);
         NOALLOC_TRY(cudaGetLastError());
     }
     return CKL_OK;
@@ -193,8 +197,13 @@ int ckl_gemm_streamk_noalloc(int ab_dtype, const void* a, const void* b, void* c
     if (a == nullptr || b == nullptr || c == nullptr) {
         return fail(CKL_ERR_INVALID_ARG, "A, B or C is null");
     }
-    if (k <= 0 || lda < k || ldb < n || ldc < n) {
-        return fail(CKL_ERR_INVALID_ARG, "need k > 0, lda >= k, ldb >= n, ldc >= n");
+    if (k <= 0) {
+        return fail(CKL_ERR_UNSUPPORTED,
+                    "this entry point only runs the tensor-core kernel, which needs k > 0 (use "
+                    "ckl_gemm_ex for C = beta*C)");
+    }
+    if (lda < k || ldb < n || ldc < n) {
+        return fail(CKL_ERR_INVALID_ARG, "need lda >= k, ldb >= n, ldc >= n");
     }
     if (reinterpret_cast<uintptr_t>(a) % 16 != 0 || reinterpret_cast<uintptr_t>(b) % 16 != 0 ||
         lda % 8 != 0 || ldb % 8 != 0) {
@@ -270,6 +279,27 @@ int ckl_gemm_streamk_noalloc(int ab_dtype, const void* a, const void* b, void* c
         case CKL_F16: return launch<__half>(ta, tb, tc, p, plan.grid, s);
         default: return launch<__nv_bfloat16>(ta, tb, tc, p, plan.grid, s);
     }
+}
+
+int ckl_noalloc_device_status(unsigned int* info) {
+    DeviceState* st = nullptr;
+    if (const int rc = set_up(&st); rc != CKL_OK) {
+        return rc;
+    }
+    NOALLOC_TRY(cudaDeviceSynchronize());
+    unsigned int words[4] = {0, 0, 0, 0};
+    NOALLOC_TRY(cudaMemcpy(words, st->status, sizeof words, cudaMemcpyDeviceToHost));
+    if (info != nullptr) {
+        std::memcpy(info, words, sizeof words);
+    }
+    if (words[0] != 0) {
+        NOALLOC_TRY(cudaMemset(st->status, 0, sizeof words));
+        return fail(CKL_ERR_DEVICE,
+                    "a kernel of ckl_gemm_streamk_noalloc gave up a bounded wait: code=%u block=%u "
+                    "role=%u detail=0x%x; C of that call is incomplete",
+                    words[0], words[1], words[2], words[3]);
+    }
+    return CKL_OK;
 }
 
 const char* ckl_noalloc_last_error(void) { return g_message; }

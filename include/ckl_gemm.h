@@ -206,11 +206,21 @@ int ckl_assemble_column_blocks(void* dst, const void* src, int elem_size, int m,
  *     them with events.
  *   - The first call on each device does one-time set-up with that device
  *     current (symbol address look-ups, kernel attributes, driver entry point);
- *     make it before any stream capture starts.
- * Errors of this entry point are described by ckl_noalloc_last_error(). */
+ *     make it before any stream capture starts.  It is also the moment the
+ *     CUDA runtime loads this library's device code on that GPU and backs the
+ *     built-in scratch with device memory (about 37 MiB): a host that gives
+ *     all device memory to its own arena makes this first call before it does.
+ *   - A wait that ran out inside one of this entry point's kernels is reported
+ *     by ckl_noalloc_device_status() (same contract as ckl_device_status():
+ *     synchronises the current device, fills the optional 4 words, clears the
+ *     word, returns CKL_OK or CKL_ERR_DEVICE), which allocates nothing either.
+ *     ckl_device_status() does not see it: that one reads the regular entry
+ *     points' word and creates their per-device context with cudaMalloc.
+ * Errors of these functions are described by ckl_noalloc_last_error(). */
 int ckl_gemm_streamk_noalloc(int ab_dtype, const void* a, const void* b, void* c, int c_dtype,
                              int m, int n, int k, int lda, int ldb, int ldc, float alpha,
                              float beta, ckl_stream_t stream);
+int ckl_noalloc_device_status(unsigned int* info);
 const char* ckl_noalloc_last_error(void);
 size_t ckl_noalloc_scratch_bytes(void);
 
