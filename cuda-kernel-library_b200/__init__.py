@@ -212,6 +212,35 @@ def plan_gemm(m, n, k, lda=None, ldb=None, ldc=None, a_align=16, b_align=16, alg
     return plan
 
 
+_lib.ckl_plan_gemm_ex.argtypes = [_i] * 13 + [ctypes.POINTER(Plan)]
+_lib.ckl_plan_gemm_ex.restype = ctypes.c_int
+_lib.ckl_last_plan.argtypes = [ctypes.POINTER(Plan)]
+_lib.ckl_last_plan.restype = ctypes.c_int
+_lib.ckl_debug_counter.argtypes = [ctypes.c_char_p]
+_lib.ckl_debug_counter.restype = ctypes.c_ulonglong
+
+
+def plan_gemm_ex(m, n, k, lda=None, ldb=None, ldc=None, a_align=16, b_align=16, algo=ALGO_AUTO,
+                 sm_count=148, max_pairs=0, c_dtype=BF16, c_is_read=False) -> Plan:
+    """plan_gemm with the output type, whether C is read and the resident CTA-pair count."""
+    plan = Plan()
+    _check(_lib.ckl_plan_gemm_ex(m, n, k, k if lda is None else lda, n if ldb is None else ldb,
+                                 n if ldc is None else ldc, a_align, b_align, algo, sm_count,
+                                 max_pairs, c_dtype, 1 if c_is_read else 0, ctypes.byref(plan)))
+    return plan
+
+
+def last_plan() -> Plan:
+    """What the calling thread's last gemm call launched (on the real device)."""
+    plan = Plan()
+    _check(_lib.ckl_last_plan(ctypes.byref(plan)))
+    return plan
+
+
+def debug_counter(name: str) -> int:
+    return int(_lib.ckl_debug_counter(name.encode()))
+
+
 def plan_sk_range(plan: Plan, unit: int) -> tuple[int, int]:
     b, e = ctypes.c_longlong(), ctypes.c_longlong()
     _check(_lib.ckl_plan_sk_range(ctypes.byref(plan), unit, ctypes.byref(b), ctypes.byref(e)))
@@ -254,6 +283,110 @@ def device_status() -> list[int]:
 
 def stream_copy(dst, src, nbytes: int, stream=None) -> None:
     _check(_lib.ckl_stream_copy(_ptr(dst), _ptr(src), nbytes, _stream(stream)))
+
+
+# --- several GPUs of one box: communicator, host-buffer sharded GEMM, gathered GEMM -----------
+
+COMM_ID_BYTES = 128
+
+
+class HostShardPlan(ctypes.Structure):
+    _fields_ = [("rows_per_rank", _i), ("row0", _i), ("rows", _i), ("panels", _i),
+                ("panel_rows", _i), ("padded_rows", _i)]
+
+
+_lib.ckl_column_shard.argtypes = [_i, _i, _i, _i, ctypes.POINTER(_i), ctypes.POINTER(_i)]
+_lib.ckl_plan_host_sharded.argtypes = [_i, _i, _i, ctypes.POINTER(HostShardPlan)]
+_lib.ckl_comm_get_unique_id.argtypes = [_vp]
+_lib.ckl_comm_init.argtypes = [ctypes.POINTER(_vp), _i, _i, _vp]
+_lib.ckl_comm_world.argtypes = [_vp]
+_lib.ckl_comm_rank.argtypes = [_vp]
+_lib.ckl_comm_destroy.argtypes = [_vp]
+_lib.ckl_comm_alloc_shared.argtypes = [_vp, ctypes.c_size_t, ctypes.POINTER(_vp)]
+_lib.ckl_comm_free_shared.argtypes = [_vp, _vp]
+_lib.ckl_gemm_host_sharded.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f]
+_lib.ckl_gemm_gathered.argtypes = [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp]
+_lib.ckl_scatter_column_block.argtypes = [ctypes.POINTER(_vp), _i, _vp, _i, _i, _i, _i, _i, _vp]
+for _name in ("ckl_column_shard", "ckl_plan_host_sharded", "ckl_comm_get_unique_id", "ckl_comm_init",
+              "ckl_comm_world", "ckl_comm_rank", "ckl_comm_destroy", "ckl_comm_alloc_shared",
+              "ckl_comm_free_shared", "ckl_gemm_host_sharded", "ckl_gemm_gathered",
+              "ckl_scatter_column_block"):
+    getattr(_lib, _name).restype = ctypes.c_int
+
+
+def column_shard(n: int, world: int, rank: int, align: int = 8) -> tuple[int, int]:
+    """(first column, width) of rank `rank`'s column block; the C form of sharded.column_shard."""
+    col0, width = _i(), _i()
+    _check(_lib.ckl_column_shard(n, world, rank, align, ctypes.byref(col0), ctypes.byref(width)))
+    return col0.value, width.value
+
+
+def plan_host_sharded(m: int, world: int, rank: int) -> HostShardPlan:
+    """Which rows of A rank `rank` uploads in gemm_host_sharded, and in how many panels."""
+    plan = HostShardPlan()
+    _check(_lib.ckl_plan_host_sharded(m, world, rank, ctypes.byref(plan)))
+    return plan
+
+
+def comm_unique_id() -> bytes:
+    """Drawn on rank 0 and handed to every rank (any transport) before Comm(...)."""
+    buf = ctypes.create_string_buffer(COMM_ID_BYTES)
+    _check(_lib.ckl_comm_get_unique_id(buf))
+    return buf.raw
+
+
+class Comm:
+    """The ranks of one job (one rank per GPU; the current device is the rank's).  Collective
+    to create and to close."""
+
+    def __init__(self, world: int, rank: int, unique_id: bytes | None = None):
+        handle = _vp()
+        uid = None
+        if unique_id is not None:
+            if len(unique_id) != COMM_ID_BYTES:
+                raise ValueError(f"unique_id must be {COMM_ID_BYTES} bytes")
+            uid = ctypes.create_string_buffer(bytes(unique_id), COMM_ID_BYTES)
+        _check(_lib.ckl_comm_init(ctypes.byref(handle), world, rank, uid))
+        self._h = handle
+        self.world, self.rank = world, rank
+
+    def alloc_shared(self, nbytes: int) -> int:
+        """A buffer of nbytes on every rank, every copy mapped into every rank; returns this
+        rank's device address.  Collective."""
+        out = _vp()
+        _check(_lib.ckl_comm_alloc_shared(self._h, nbytes, ctypes.byref(out)))
+        return int(out.value)
+
+    def free_shared(self, ptr: int) -> None:
+        _check(_lib.ckl_comm_free_shared(self._h, ptr))
+
+    def gemm_host_sharded(self, ab_dtype, a_rows_host, b_shard_host, c_shard_host, c_dtype, m,
+                          n_shard, k, alpha, beta) -> None:
+        """N-sharded GEMM on host buffers: this rank's rows of A, its blocks of B and C."""
+        _check(_lib.ckl_gemm_host_sharded(self._h, ab_dtype, _ptr(a_rows_host), _ptr(b_shard_host),
+                                          _ptr(c_shard_host), c_dtype, m, n_shard, k, alpha, beta))
+
+    def gemm_gathered(self, ab_dtype, a, b_shard, c_shard, c_full, c_dtype, m, n, k, lda, ldb,
+                      alpha, beta, stream=None) -> None:
+        """N-sharded GEMM on device buffers; c_full (from alloc_shared) ends with the whole C on
+        every rank."""
+        _check(_lib.ckl_gemm_gathered(self._h, ab_dtype, _ptr(a), _ptr(b_shard), _ptr(c_shard),
+                                      _ptr(c_full), c_dtype, m, n, k, lda, ldb, alpha, beta,
+                                      _stream(stream)))
+
+    def close(self) -> None:
+        if self._h is not None and self._h.value:
+            _check(_lib.ckl_comm_destroy(self._h))
+            self._h = None
+
+
+def scatter_column_block(dsts, src, elem_size: int, rows: int, width: int, n: int, col0: int,
+                         stream=None) -> None:
+    """Write the packed rows x width block src to columns [col0, col0 + width) of each row-major
+    rows x n matrix in dsts."""
+    arr = (_vp * len(dsts))(*[_ptr(d) for d in dsts])
+    _check(_lib.ckl_scatter_column_block(arr, len(dsts), _ptr(src), elem_size, rows, width, n, col0,
+                                         _stream(stream)))
 
 
 _lib.ckl_gemm_streamk_noalloc.argtypes = [_i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]

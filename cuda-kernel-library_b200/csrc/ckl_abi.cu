@@ -5,6 +5,7 @@
 // needed (cuTensorMapEncodeTiled) is fetched through the runtime.
 
 #include <algorithm>
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -21,6 +22,7 @@
 #include <cuda_runtime.h>
 
 #include "ckl_gemm.h"
+#include "ckl_internal.h"
 #include "gemm_fp32.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_umma.cuh"
@@ -28,10 +30,24 @@
 #include "trsm.cuh"
 
 namespace {
+thread_local std::string g_last_error;
+}  // namespace
+
+namespace ckl {
+int set_error(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+}  // namespace ckl
+
+namespace {
 
 using namespace ckl;
-
-thread_local std::string g_last_error;
 
 int fail(int code, const char* fmt, ...) {
     char buf[512];
@@ -63,6 +79,25 @@ struct Staging {
     unsigned int epoch = 0;  // stream-K workspaces: value of the "partial is ready" flags of the last launch
 };
 
+// One encoded TMA descriptor and what it was encoded from.  A descriptor is a pure function of
+// these fields, so an entry stays valid for as long as a buffer with that address and shape is
+// what the caller passes, whoever allocated it.
+struct MapKey {
+    const void* base;
+    uint64_t inner, outer, pitch;
+    int dtype;
+    uint32_t box_inner, box_outer;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && inner == o.inner && outer == o.outer && pitch == o.pitch &&
+               dtype == o.dtype && box_inner == o.box_inner && box_outer == o.box_outer;
+    }
+};
+struct MapEntry {
+    MapKey key = {};
+    CUtensorMap map = {};
+    uint64_t stamp = 0;  // 0 = empty; else the clock value of the last use
+};
+
 struct DeviceCtx {
     int device = -1;
     int sm_count = 0;
@@ -79,8 +114,16 @@ struct DeviceCtx {
     cudaEvent_t host_events[2 * kHostPanels] = {};  // per panel: uploaded, computed
     std::mutex host_mu;                        // one ckl_gemm_host call at a time per device
     bool attrs_set = false;
+    // Recently used TMA descriptors (least recently used entry is replaced).  Encoding one
+    // costs a driver call; a small GEMM launched in a loop would otherwise pay three per call.
+    static constexpr int kMapCache = 48;
+    MapEntry map_cache[kMapCache];
+    uint64_t map_clock = 0;
     std::mutex mu;
 };
+
+std::atomic<unsigned long long> g_tensor_map_encodes{0};
+thread_local ckl_plan g_last_plan = {};
 
 std::mutex g_ctx_mu;
 std::map<int, std::unique_ptr<DeviceCtx>> g_ctx;
@@ -205,6 +248,25 @@ struct Plan {
     Schedule sched = {};
     size_t workspace_bytes = 0;
 };
+
+// Plan -> the public struct
+void export_plan(const Plan& plan, ckl_plan* out) {
+    out->algo = plan.algo;
+    out->tile_m = plan.tile_m;
+    out->tile_n = plan.tile_n;
+    out->tile_k = plan.tile_k;
+    out->tiles_m = plan.sched.tiles_m;
+    out->tiles_n = plan.sched.tiles_n;
+    out->k_blocks = plan.sched.k_blocks;
+    out->grid = plan.grid;
+    out->units = plan.sched.units;
+    out->group_m = plan.sched.group_m;
+    out->dp_tiles = plan.sched.dp_tiles;
+    out->sk_tiles = plan.sched.sk_tiles;
+    out->sk_units = plan.sched.sk_tiles > 0 ? plan.sched.units : 0;
+    out->sk_iters = plan.sched.sk_iters;
+    out->workspace_bytes = plan.workspace_bytes;
+}
 
 bool tma_legal(int k, int lda, int ldb, size_t a_align, size_t b_align) {
     return k > 0 && lda % 8 == 0 && ldb % 8 == 0 && a_align % 16 == 0 && b_align % 16 == 0;
@@ -372,8 +434,38 @@ int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_al
 
 // ---- TMA descriptors -----------------------------------------------------------
 
+int encode_2d_uncached(DeviceCtx* ctx, CUtensorMap* map, int dtype, const void* base, uint64_t inner,
+                       uint64_t outer, uint64_t pitch_elems, uint32_t box_inner, uint32_t box_outer);
+
 int encode_2d(DeviceCtx* ctx, CUtensorMap* map, int dtype, const void* base, uint64_t inner,
               uint64_t outer, uint64_t pitch_elems, uint32_t box_inner, uint32_t box_outer) {
+    const MapKey key = {base, inner, outer, pitch_elems, dtype, box_inner, box_outer};
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    MapEntry* victim = &ctx->map_cache[0];
+    for (MapEntry& e : ctx->map_cache) {
+        if (e.stamp != 0 && e.key == key) {
+            e.stamp = ++ctx->map_clock;
+            *map = e.map;
+            return CKL_OK;
+        }
+        if (e.stamp < victim->stamp) {
+            victim = &e;
+        }
+    }
+    if (const int rc = encode_2d_uncached(ctx, map, dtype, base, inner, outer, pitch_elems, box_inner,
+                                          box_outer);
+        rc != CKL_OK) {
+        return rc;
+    }
+    victim->key = key;
+    victim->map = *map;
+    victim->stamp = ++ctx->map_clock;
+    return CKL_OK;
+}
+
+int encode_2d_uncached(DeviceCtx* ctx, CUtensorMap* map, int dtype, const void* base, uint64_t inner,
+                       uint64_t outer, uint64_t pitch_elems, uint32_t box_inner, uint32_t box_outer) {
+    g_tensor_map_encodes.fetch_add(1, std::memory_order_relaxed);
     const cuuint64_t dims[2] = {inner, outer};
     const cuuint64_t strides[1] = {pitch_elems * dtype_size(dtype)};
     const cuuint32_t box[2] = {box_inner, box_outer};
@@ -588,6 +680,7 @@ int gemm_impl(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, 
         rc != CKL_OK) {
         return rc;
     }
+    export_plan(plan, &g_last_plan);
     if (plan.algo == CKL_ALGO_SIMT) {
         return ab_dtype == CKL_F16
                    ? launch_simt_in<__half>(c_dtype, a, b, c, bias, m, n, k, lda, ldb, ldc, alpha,
@@ -947,12 +1040,16 @@ int ckl_gemm_host(int ab_dtype, const void* a_host, const void* b_host, void* c_
     return CKL_OK;
 }
 
-int ckl_plan_gemm(int m, int n, int k, int lda, int ldb, int ldc, int a_align, int b_align,
-                  int algo, int sm_count, ckl_plan* out) {
+int ckl_plan_gemm_ex(int m, int n, int k, int lda, int ldb, int ldc, int a_align, int b_align,
+                     int algo, int sm_count, int max_pairs, int c_dtype, int c_is_read,
+                     ckl_plan* out) {
     if (out == nullptr) {
         return fail(CKL_ERR_INVALID_ARG, "ckl_plan_gemm: out is null");
     }
     std::memset(out, 0, sizeof *out);
+    if (c_dtype != CKL_F32 && c_dtype != CKL_F16 && c_dtype != CKL_BF16) {
+        return fail(CKL_ERR_INVALID_ARG, "C dtype must be CKL_F32, CKL_F16 or CKL_BF16 (got %d)", c_dtype);
+    }
     if (m <= 0 || n <= 0 || k <= 0) {
         out->algo = CKL_ALGO_SIMT;  // degenerate: no tiles (k <= 0 runs the scale kernel)
         return CKL_OK;
@@ -961,28 +1058,35 @@ int ckl_plan_gemm(int m, int n, int k, int lda, int ldb, int ldc, int a_align, i
         return fail(CKL_ERR_INVALID_ARG, "leading dimension smaller than the row length");
     }
     Plan plan;
+    const int c_traffic = static_cast<int>(dtype_size(c_dtype)) * (c_is_read ? 2 : 1);
     if (const int rc = make_plan(m, n, k, lda, ldb, static_cast<size_t>(a_align),
-                                 static_cast<size_t>(b_align), algo, sm_count, sm_count / 2,
-                                 /*c_traffic=*/2, &plan);
+                                 static_cast<size_t>(b_align), algo, sm_count,
+                                 max_pairs > 0 ? max_pairs : sm_count / 2, c_traffic, &plan);
         rc != CKL_OK) {
         return rc;
     }
-    out->algo = plan.algo;
-    out->tile_m = plan.tile_m;
-    out->tile_n = plan.tile_n;
-    out->tile_k = plan.tile_k;
-    out->tiles_m = plan.sched.tiles_m;
-    out->tiles_n = plan.sched.tiles_n;
-    out->k_blocks = plan.sched.k_blocks;
-    out->grid = plan.grid;
-    out->units = plan.sched.units;
-    out->group_m = plan.sched.group_m;
-    out->dp_tiles = plan.sched.dp_tiles;
-    out->sk_tiles = plan.sched.sk_tiles;
-    out->sk_units = plan.sched.sk_tiles > 0 ? plan.sched.units : 0;
-    out->sk_iters = plan.sched.sk_iters;
-    out->workspace_bytes = plan.workspace_bytes;
+    export_plan(plan, out);
     return CKL_OK;
+}
+
+int ckl_plan_gemm(int m, int n, int k, int lda, int ldb, int ldc, int a_align, int b_align,
+                  int algo, int sm_count, ckl_plan* out) {
+    return ckl_plan_gemm_ex(m, n, k, lda, ldb, ldc, a_align, b_align, algo, sm_count, 0, CKL_BF16, 0, out);
+}
+
+int ckl_last_plan(ckl_plan* out) {
+    if (out == nullptr) {
+        return fail(CKL_ERR_INVALID_ARG, "ckl_last_plan: out is null");
+    }
+    *out = g_last_plan;
+    return CKL_OK;
+}
+
+unsigned long long ckl_debug_counter(const char* name) {
+    if (name != nullptr && std::strcmp(name, "tensor_map_encodes") == 0) {
+        return g_tensor_map_encodes.load(std::memory_order_relaxed);
+    }
+    return ~0ull;
 }
 
 int ckl_plan_sk_range(const ckl_plan* plan, int u, long long* begin, long long* end) {

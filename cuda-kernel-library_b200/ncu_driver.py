@@ -57,9 +57,24 @@ def main() -> None:
         print(f"sgemm {m}x{n}x{k} fp32 beta={args.beta}: {ms:.4f} ms, "
               f"{2.0 * m * n * k / ms / 1e9:.2f} TFLOP/s (last of {args.iters} launches)")
         return
+    if args.algo == "trsm":
+        # the blocked triangular solve: m x m lower triangle, n right-hand sides (k is ignored)
+        m, n = args.m, args.n
+        l = torch.tril(torch.randn(m, m, device="cuda")) + 4.0 * torch.eye(m, device="cuda")
+        b0 = torch.randn(m, n, device="cuda")
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(args.iters):
+            b = b0.clone()
+            e0.record()
+            ckl.strsm_lower(l, b, m, n, alpha=args.alpha)
+            e1.record()
+        torch.cuda.synchronize()
+        print(f"trsm {m}x{m}, {n} right-hand sides: {e0.elapsed_time(e1):.4f} ms "
+              f"(last of {args.iters} solves)")
+        return
     algos = {ckl.algo_name(i): i for i in range(ckl.NUM_ALGOS)}
     if args.algo not in algos:
-        raise SystemExit(f"--algo must be one of {sorted(algos) + ['sgemm']}")
+        raise SystemExit(f"--algo must be one of {sorted(algos) + ['sgemm', 'trsm']}")
     tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
     cdt = {"f16": ckl.F16, "bf16": ckl.BF16, "f32": ckl.F32}
     m, n, k = args.m, args.n, args.k

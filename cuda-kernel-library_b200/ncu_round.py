@@ -4,8 +4,14 @@ Counterpart of the reference's benchmarks/run_ncu_round.sh:40-81: for every "var
 pair, profile one settled launch of that kernel with a curated set of sections and keep the
 report, a readable detail page and a record of the commit, toolkit and driver.
 
-    python cuda-kernel-library_b200/ncu_round.py <round_name> <variant:size> [variant:size ...]
+    python cuda-kernel-library_b200/ncu_round.py <round_name> <variant:size[:kernel]> [...]
     e.g.  ncu_round.py wide_vs_pair umma_2cta_wide:8192 umma_2cta:8192 umma_1cta:4096
+          ncu_round.py shard umma_2cta_wide:8192x1024x8192 --beta 0.5
+          ncu_round.py fixup umma_1cta_streamk:1024x1024x32768:streamk_fixup_kernel
+
+`size` is one number (a cube) or MxNxK; `kernel` overrides the kernel-name filter (default:
+umma_gemm_kernel; sgemm_kernel, simt_gemm_kernel and trsm_diag_block_kernel for the variants
+sgemm, simt and trsm).
 
 Output: <out>/<round_name>/<variant>_<size>.ncu-rep, the matching .txt (details page) and
 round_meta.txt; <out> defaults to ./ncu_rounds (--out to change).
@@ -46,8 +52,26 @@ def tool_output(cmd: list[str]) -> str:
         return "unknown"
 
 
-def driver_command(variant: str, size: int, dtype: str, beta: float) -> list[str]:
-    return [sys.executable, DRIVER, "--m", str(size), "--n", str(size), "--k", str(size), "--in", dtype,
+DEFAULT_KERNEL = {"sgemm": "sgemm_kernel", "simt": "simt_gemm_kernel", "trsm": "trsm_diag_block_kernel"}
+
+
+def parse_pair(pair: str) -> tuple[str, tuple[int, int, int], str]:
+    """"variant:size[:kernel]" -> (variant, (m, n, k), kernel-name filter)."""
+    fields = pair.split(":")
+    if len(fields) not in (2, 3) or not fields[0]:
+        raise ValueError(f"expected variant:size[:kernel], got {pair!r}")
+    dims = [int(x) for x in fields[1].lower().split("x")]
+    if len(dims) == 1:
+        dims = dims * 3
+    if len(dims) != 3 or min(dims) <= 0:
+        raise ValueError(f"size must be N or MxNxK with positive numbers, got {fields[1]!r}")
+    kernel = fields[2] if len(fields) == 3 else DEFAULT_KERNEL.get(fields[0], "umma_gemm_kernel")
+    return fields[0], (dims[0], dims[1], dims[2]), kernel
+
+
+def driver_command(variant: str, shape: tuple[int, int, int], dtype: str, beta: float) -> list[str]:
+    m, n, k = shape
+    return [sys.executable, DRIVER, "--m", str(m), "--n", str(n), "--k", str(k), "--in", dtype,
             "--out", dtype, "--beta", str(beta), "--algo", variant, "--iters", "3"]
 
 
@@ -74,16 +98,16 @@ def main() -> int:
 
     failures = 0
     for pair in args.pairs:
-        variant, _, size_text = pair.partition(":")
-        size = int(size_text)
-        kernel = "sgemm_kernel" if variant == "sgemm" else "umma_gemm_kernel"
-        base = os.path.join(out_dir, f"{variant}_{size}")
-        cmd = driver_command(variant, size, args.dtype, args.beta)
+        variant, shape, kernel = parse_pair(pair)
+        size = str(shape[0]) if shape[0] == shape[1] == shape[2] else "x".join(map(str, shape))
+        base = os.path.join(out_dir, f"{variant}_{size}" +
+                            ("" if kernel in ("umma_gemm_kernel", DEFAULT_KERNEL.get(variant)) else f"_{kernel}"))
+        cmd = driver_command(variant, shape, args.dtype, args.beta)
         # Split schedules are profiled in their two-kernel form: under the profiler's kernel
         # replay the cooperative launch of the fused form ended with a launch failure reported
         # by the driver, while the same command passes on its own.
         os.environ["CKL_STREAMK_FIXUP"] = "pass"
-        print(f"profiling {variant} at {size} cubed (kernel {kernel})", flush=True)
+        print(f"profiling {variant} at {size} (kernel {kernel})", flush=True)
         plain = subprocess.run(cmd, capture_output=True, text=True)
         if plain.returncode != 0:
             print(f"  not profiled: the plain run exited {plain.returncode}\n{plain.stderr[-800:]}")
@@ -92,6 +116,8 @@ def main() -> int:
         ncu = [args.ncu, "--clock-control", "none"]
         for section in SECTIONS:
             ncu += ["--section", section]
+        # skip the two warm launches of the driver; trsm launches several diagonal-block kernels
+        # per solve, any settled one serves
         ncu += ["--kernel-name", f"regex:{kernel}", "--launch-skip", "2", "--launch-count", "1",
                 "--force-overwrite", "--export", base, *cmd]
         run = subprocess.run(ncu, capture_output=True, text=True)

@@ -15,6 +15,14 @@ gathered [rank][row][col] blocks into row-major [row][all cols].
 this library's CUDA kernels, reached through the C ABI.  The two callables can
 be replaced (tests on CPU ranks inject host stand-ins to exercise the shard
 arithmetic and the collective without a GPU); the defaults have no fallback.
+
+Two further operations go through the library's own communicator (`ckl.Comm`,
+NCCL bound inside the C library) and need no process group at all:
+`ShardedGemm.gathered` assembles C with the library's copy kernel writing each
+row panel straight into every rank's C while the next panel multiplies, and
+`ShardedGemm.run_host` is the whole operation on host buffers, every rank
+uploading only its own rows of A.  `make_comm` builds the communicator from a
+`torch.distributed` group when there is one.
 """
 
 from __future__ import annotations
@@ -94,8 +102,51 @@ class ShardedGemm:
             raise ValueError(
                 f"gather needs equal column blocks: n={self.n} is not a multiple of "
                 f"world*8={self.shard.world * 8}")
-        # [world][m][width] is the row-wise concatenation of the ranks' [m][width] blocks
-        dist.all_gather_into_tensor(staging.view(self.shard.world * self.m, self.shard.width),
-                                    c_shard, group=group)
+        # [world][m][width] is the row-wise concatenation of the ranks' [m][width] blocks.
+        # The collective is ordered against torch's CURRENT stream only, so it is issued with
+        # `stream` current: behind the GEMM that wrote c_shard, ahead of the interleave.
+        flat = staging.view(self.shard.world * self.m, self.shard.width)
+        if stream is not None and hasattr(stream, "cuda_stream"):
+            import torch
+            with torch.cuda.stream(stream):
+                dist.all_gather_into_tensor(flat, c_shard, group=group)
+        else:
+            if stream is not None and c_shard.is_cuda:
+                import torch
+                if int(stream) != torch.cuda.current_stream().cuda_stream:
+                    raise ValueError("gather: pass a torch stream, or make `stream` the current "
+                                     "stream; a raw handle of another stream cannot be ordered "
+                                     "against the collective")
+            dist.all_gather_into_tensor(flat, c_shard, group=group)
         self._assemble(out_full, staging, c_shard.element_size(), self.m, self.shard.width,
                        self.shard.world, stream)
+
+    def gathered(self, comm, a, b_shard, c_shard, c_full, alpha: float, beta: float, *, lda=None,
+                 ldb=None, stream=None) -> None:
+        """GEMM and assembly in one call of the C library (ckl_gemm_gathered): `c_full` is a
+        buffer from `comm.alloc_shared`; every rank ends with the row-major m x n matrix."""
+        comm.gemm_gathered(self.ab_dtype, a, b_shard, c_shard, c_full, self.c_dtype, self.m, self.n,
+                           self.k, self.k if lda is None else lda,
+                           self.shard.width if ldb is None else ldb, alpha, beta, stream)
+
+    def run_host(self, comm, a_rows_host, b_shard_host, c_shard_host, alpha: float, beta: float) -> None:
+        """The whole operation on HOST buffers (ckl_gemm_host_sharded): `a_rows_host` holds only
+        the rows of A that `ckl.plan_host_sharded(m, world, rank)` assigns to this rank."""
+        comm.gemm_host_sharded(self.ab_dtype, a_rows_host, b_shard_host, c_shard_host, self.c_dtype,
+                               self.m, self.shard.width, self.k, alpha, beta)
+
+
+def make_comm(ckl, world: int, rank: int, group=None, device=None):
+    """A `ckl.Comm` for the ranks of a torch.distributed group: rank 0 draws the id, a
+    broadcast carries it.  With world == 1 no process group is needed."""
+    if world == 1:
+        return ckl.Comm(1, 0, None)
+    import torch
+    import torch.distributed as dist
+    uid = torch.zeros(ckl.COMM_ID_BYTES, dtype=torch.uint8)
+    if rank == 0:
+        uid = torch.frombuffer(bytearray(ckl.comm_unique_id()), dtype=torch.uint8).clone()
+    if device is not None:
+        uid = uid.to(device)
+    dist.broadcast(uid, src=0, group=group)
+    return ckl.Comm(world, rank, bytes(uid.cpu().numpy().tobytes()))

@@ -151,6 +151,17 @@ typedef struct ckl_plan {
 int ckl_plan_gemm(int m, int n, int k, int lda, int ldb, int ldc, int a_align, int b_align,
                   int algo, int sm_count, ckl_plan* out);
 
+/* The same with everything the dispatcher looks at: the C type, whether C is read
+ * (beta != 0 without the bias epilogue) and the number of CTA pairs the device can keep
+ * resident (max_pairs <= 0 means sm_count / 2, the usual value). */
+int ckl_plan_gemm_ex(int m, int n, int k, int lda, int ldb, int ldc, int a_align, int b_align,
+                     int algo, int sm_count, int max_pairs, int c_dtype, int c_is_read,
+                     ckl_plan* out);
+
+/* The plan of the calling thread's most recent ckl_gemm_* call that reached the dispatcher:
+ * what was actually launched, on the actual device. */
+int ckl_last_plan(ckl_plan* out);
+
 /* The k-block range of split tile work owned by unit `u` of a plan:
  * iterations [*begin, *end) of the sk_iters total.  Exposed for tests. */
 int ckl_plan_sk_range(const ckl_plan* plan, int u, long long* begin, long long* end);
@@ -185,6 +196,84 @@ int ckl_stream_copy(void* dst, const void* src, size_t bytes, ckl_stream_t strea
  * row-major m x (parts * n_shard) matrix dst.  elem_size is 2 or 4 bytes. */
 int ckl_assemble_column_blocks(void* dst, const void* src, int elem_size, int m, int n_shard,
                                int parts, ckl_stream_t stream);
+
+/* ---- several GPUs of one box (no counterpart in the reference, which is single-GPU and
+ * never calls cudaSetDevice; its upload / launch / download sequence,
+ * tests/test_gemm_tensor.cpp:69-85, is what these generalise) ---------------------------
+ *
+ * One rank per GPU, each a process or a host thread with its device current.  Output columns
+ * are independent, so rank r of `world` owns the column block ckl_column_shard() gives it of
+ * B and C, and A is replicated.  The ranks meet through a communicator that wraps NCCL
+ * (loaded with dlopen at first use: the library itself still links only the CUDA runtime;
+ * CKL_NCCL_LIB names the file if "libnccl.so.2" is not on the loader's path).  Every NCCL
+ * call gets buffers of the calling rank's own memory; the only accesses to another GPU's
+ * memory are plain stores of this library's copy kernel into buffers made with
+ * ckl_comm_alloc_shared. */
+
+/* Column block of rank `rank`: block widths are multiples of `align` columns (8 keeps every
+ * block 16-byte aligned for 16-bit types), the tail rank takes what is left, ranks past the
+ * end get width 0. */
+int ckl_column_shard(int n, int world, int rank, int align, int* col0, int* width);
+
+typedef struct ckl_comm ckl_comm;
+#define CKL_COMM_ID_BYTES 128
+
+/* Rank 0 draws an id (CKL_COMM_ID_BYTES bytes) and hands it to the other ranks by any means
+ * the job has; then every rank calls ckl_comm_init with its device current.  Collective. */
+int ckl_comm_get_unique_id(void* id);
+int ckl_comm_init(ckl_comm** comm, int world, int rank, const void* id);
+int ckl_comm_world(const ckl_comm* comm);
+int ckl_comm_rank(const ckl_comm* comm);
+/* Frees the communicator's streams, staging and shared buffers.  Collective when world > 1. */
+int ckl_comm_destroy(ckl_comm* comm);
+
+/* A device buffer of `bytes` bytes on every rank, each rank's copy mapped into all the others
+ * (CUDA IPC between processes, peer access between threads of one process).  Collective: all
+ * ranks call it with the same size, in the same order.  *local is this rank's copy. */
+int ckl_comm_alloc_shared(ckl_comm* comm, size_t bytes, void** local);
+int ckl_comm_free_shared(ckl_comm* comm, void* local);
+
+/* How ckl_gemm_host_sharded deals the m rows of A: rank r uploads rows
+ * [row0, row0 + rows) (rows_per_rank each, the tail rank fewer), in `panels` panels of
+ * panel_rows rows; on the device A and C live as [panel][rank][panel_rows] rows
+ * (padded_rows in all).  Pure host arithmetic. */
+typedef struct ckl_host_shard_plan {
+    int rows_per_rank;
+    int row0, rows;
+    int panels, panel_rows;
+    int padded_rows;
+} ckl_host_shard_plan;
+int ckl_plan_host_sharded(int m, int world, int rank, ckl_host_shard_plan* out);
+
+/* The N-sharded GEMM on HOST buffers, end to end: C[:, block] = alpha*A*B[:, block] +
+ * beta*C[:, block].  a_rows_host is THIS rank's rows of A (plan.rows x k, packed), so the m x k
+ * matrix crosses the host links once in total, not once per GPU; b_shard_host is the rank's
+ * k x n_shard block and c_shard_host its m x n_shard block (both packed).  Each rank uploads
+ * over its own link, the row panels of A are all-gathered over NVLink, and panel j is
+ * multiplied and sent back while panel j+1 is still arriving.  Collective; returns when this
+ * rank's block of C is in c_shard_host.  With world == 1 it is ckl_gemm_host. */
+int ckl_gemm_host_sharded(ckl_comm* comm, int ab_dtype, const void* a_rows_host,
+                          const void* b_shard_host, void* c_shard_host, int c_dtype, int m,
+                          int n_shard, int k, float alpha, float beta);
+
+/* The N-sharded GEMM on DEVICE buffers with the whole C assembled on every rank.  a is the
+ * replicated m x k matrix (lda), b_shard the rank's k x width block (ldb), c_shard its packed
+ * m x width block (C_in on entry when beta != 0, the rank's result on return), c_full a buffer
+ * from ckl_comm_alloc_shared that receives the row-major m x n matrix; width and the column
+ * offset are ckl_column_shard(n, world, rank, 8).  The local GEMM runs in row panels on
+ * `stream`; behind each panel a copy kernel writes the panel's column block into every rank's
+ * c_full with plain 16-byte stores over NVLink, on a stream of the communicator, so the
+ * transfer overlaps the next panel's multiplication.  Collective and stream-ordered: later
+ * work on `stream` sees the complete c_full of all ranks' blocks. */
+int ckl_gemm_gathered(ckl_comm* comm, int ab_dtype, const void* a, const void* b_shard,
+                      void* c_shard, void* c_full, int c_dtype, int m, int n, int k, int lda,
+                      int ldb, float alpha, float beta, ckl_stream_t stream);
+
+/* The copy kernel on its own: writes the packed rows x width block src to columns
+ * [col0, col0 + width) of `parts` row-major matrices of n columns (dsts[i], any mix of local
+ * and mapped peer buffers).  elem_size is 2 or 4 bytes. */
+int ckl_scatter_column_block(void* const* dsts, int parts, const void* src, int elem_size,
+                             int rows, int width, int n, int col0, ckl_stream_t stream);
 
 /* No counterpart in the reference.  The stream-K tensor-core GEMM for callers that
  * must not allocate device memory: hosts that have given all device memory to an
@@ -223,6 +312,11 @@ int ckl_gemm_streamk_noalloc(int ab_dtype, const void* a, const void* b, void* c
 int ckl_noalloc_device_status(unsigned int* info);
 const char* ckl_noalloc_last_error(void);
 size_t ckl_noalloc_scratch_bytes(void);
+
+/* Counters for tests: "tensor_map_encodes" = TMA descriptors encoded by this process so far
+ * (descriptors are cached per device, keyed by address, shape, pitch, type and box, so a
+ * repeated call encodes none).  Unknown names give ~0. */
+unsigned long long ckl_debug_counter(const char* name);
 
 /* Message of the calling thread's most recent non-zero status ("" if none). */
 const char* ckl_last_error(void);

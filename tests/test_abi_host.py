@@ -146,6 +146,24 @@ def test_dispatch_follows_the_reference_contract(ckl):
         assert p.sk_tiles > 0 and p.workspace_bytes > 0
 
 
+def test_plan_sees_the_output_type_and_the_pair_count(ckl):
+    """ckl_plan_gemm_ex takes what the dispatcher takes: an FP32 C that is read and written
+    keeps the 256x256 tile up to k = 8192 (the 16-bit plan switches to the wide tile at 4096),
+    and a device that keeps fewer CTA pairs resident gets a schedule for that many."""
+    wide = ckl.plan_gemm_ex(16384, 14336, 4096, c_dtype=ckl.BF16, c_is_read=True)
+    assert wide.algo == ckl.plan_gemm(16384, 14336, 4096).algo == ckl.ALGO_UMMA_2CTA_WIDE
+    f32 = ckl.plan_gemm_ex(16384, 14336, 4096, c_dtype=ckl.F32, c_is_read=True)
+    assert f32.algo in (ckl.ALGO_UMMA_2CTA, ckl.ALGO_UMMA_2CTA_SK) and f32.tile_n == 256
+    assert ckl.plan_gemm_ex(16384, 14336, 4096, c_dtype=ckl.F32, c_is_read=False).algo == wide.algo
+    assert ckl.plan_gemm_ex(16384, 14336, 8192, c_dtype=ckl.F32, c_is_read=True).tile_n == 512
+    fewer = ckl.plan_gemm_ex(8192, 8192, 8192, max_pairs=66)
+    assert fewer.units == 66 and fewer.grid == 132
+    with pytest.raises(ckl.CklError):
+        ckl.plan_gemm_ex(256, 256, 256, c_dtype=7)
+    assert ckl.debug_counter("no such counter") == 2 ** 64 - 1
+    assert ckl.debug_counter("tensor_map_encodes") == 0      # nothing was launched here
+
+
 SHAPES = [(128, 256, 64), (256, 256, 256), (4000, 3000, 5000), (1024, 1024, 32768),
           (8192, 8192, 8192), (8192, 1024, 8192), (16384, 1792, 4096), (200, 264, 72),
           (2304, 4096, 1024), (1000, 776, 520), (128, 256, 6400), (100000, 256, 64)]

@@ -448,6 +448,49 @@ def test_assemble_column_blocks(env):
         assert torch.equal(dst, src.permute(1, 0, 2).reshape(m, parts * width))
 
 
+def test_descriptors_are_cached_and_the_plan_is_reported(env):
+    """A repeated call encodes no TMA descriptor (they are cached per device by address, shape,
+    pitch, type and box), a call on other buffers encodes its own, and ckl_last_plan reports
+    what was launched: the same plan ckl_plan_gemm_ex gives for the C type and beta used."""
+    ckl = env.ckl
+    m = n = k = 512
+    a = torch.randn(m, k, device="cuda").half()
+    b = torch.randn(k, n, device="cuda").half()
+    c = torch.zeros(m, n, device="cuda")
+    ckl.gemm_ex(ckl.F16, a, b, c, ckl.F32, m, n, k, k, n, n, 1.0, 0.0)
+    first = ckl.debug_counter("tensor_map_encodes")
+    want = c.clone()
+    for _ in range(5):
+        ckl.gemm_ex(ckl.F16, a, b, c, ckl.F32, m, n, k, k, n, n, 1.0, 0.0)
+    assert ckl.debug_counter("tensor_map_encodes") == first
+    torch.cuda.synchronize()
+    assert torch.equal(c, want)
+    c2 = torch.zeros(m, n, device="cuda")
+    ckl.gemm_ex(ckl.F16, a, b, c2, ckl.F32, m, n, k, k, n, n, 1.0, 0.0)
+    assert ckl.debug_counter("tensor_map_encodes") == first + 1      # only C's descriptor is new
+    torch.cuda.synchronize()
+    assert torch.equal(c2, want)
+    # more distinct buffers than cache entries: entries are replaced, results stay right
+    outs = [torch.zeros(m, n, device="cuda") for _ in range(60)]
+    for o in outs:
+        ckl.gemm_ex(ckl.F16, a, b, o, ckl.F32, m, n, k, k, n, n, 1.0, 0.0)
+    torch.cuda.synchronize()
+    assert all(torch.equal(o, want) for o in outs)
+    # the reported plan is the launched one, FP32 C with beta != 0 included
+    mm, nn, kk = 2048, 4096, 4096
+    a = torch.randn(mm, kk, device="cuda").bfloat16()
+    b = torch.randn(kk, nn, device="cuda").bfloat16()
+    c = torch.zeros(mm, nn, device="cuda")
+    ckl.gemm_ex(ckl.BF16, a, b, c, ckl.F32, mm, nn, kk, kk, nn, nn, 1.0, 0.5)
+    got = ckl.last_plan()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    want_plan = ckl.plan_gemm_ex(mm, nn, kk, sm_count=sms, max_pairs=got.units if got.tile_m == 256 else 0,
+                                 c_dtype=ckl.F32, c_is_read=True)
+    assert (got.algo, got.tile_n, got.sk_tiles) == (want_plan.algo, want_plan.tile_n, want_plan.sk_tiles)
+    assert got.tile_n == 256          # FP32 C read and written at k = 4096: not the wide tile
+    torch.cuda.synchronize()
+
+
 def test_reference_test_driver_runs_unchanged(env):
     """The reference's own tests/test_gemm_tensor.cpp, compiled without edits against this
     repository's include/ckl headers and library (oracle/Makefile target `dropin`), passes."""

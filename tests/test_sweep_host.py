@@ -68,13 +68,19 @@ def test_ncu_round_commands(tmp_path, monkeypatch):
     fake_driver.write_text("import sys\nsys.exit(7 if 'umma_1cta' in sys.argv else 0)\n")
     monkeypatch.setattr(mod, "DRIVER", str(fake_driver))
     monkeypatch.setattr(sys, "argv", ["ncu_round.py", "r1", "umma_2cta_wide:8192", "umma_1cta:4096",
-                                      "sgemm:2048", "--out", str(tmp_path), "--ncu", str(fake_ncu)])
+                                      "sgemm:2048", "umma_2cta:8192x1024x8192",
+                                      "umma_2cta_streamk:1024x1024x32768:streamk_fixup_kernel",
+                                      "--out", str(tmp_path), "--ncu", str(fake_ncu)])
     assert mod.main() == 1                       # one configuration failed its plain run
     calls = log.read_text().splitlines()
     profiled = [c for c in calls if "--export" in c]
-    assert len(profiled) == 2 and all("--clock-control none" in c for c in profiled)
+    assert len(profiled) == 4 and all("--clock-control none" in c for c in profiled)
     assert "regex:umma_gemm_kernel" in profiled[0] and "--launch-skip 2 --launch-count 1" in profiled[0]
     assert "regex:sgemm_kernel" in profiled[1]
+    assert "--m 8192 --n 1024 --k 8192" in profiled[2] and "umma_2cta_8192x1024x8192" in profiled[2]
+    assert "regex:streamk_fixup_kernel" in profiled[3]
+    assert "umma_2cta_streamk_1024x1024x32768_streamk_fixup_kernel" in profiled[3]
+    assert mod.parse_pair("simt:129x257x193")[2] == "simt_gemm_kernel"
     assert not any("umma_1cta" in c for c in calls)
     assert (tmp_path / "r1" / "umma_2cta_wide_8192.txt").read_text().strip() == "details page"
     meta = (tmp_path / "r1" / "round_meta.txt").read_text()
