@@ -677,12 +677,20 @@ def run_mlp_sharded(torch, dist, ckl, sharded, comm, world, rank, all_max, barri
         ckl.gemm_ex(ckl.BF16, a, b_full[:, ncol0:ncol0 + nw].contiguous(), ref, ckl.BF16, m, nw, k, k, nw, nw,
                     1.0, 0.0, 0, stream)
         torch.cuda.synchronize()
-        ok = torch.equal(got[:, col0:col0 + w], c) and torch.equal(got[:, ncol0:ncol0 + nw], ref)
+        cmp = compare(torch, got[:, ncol0:ncol0 + nw], ref)
+        tol = 2e-2 * math.sqrt(k / 4096.0) * cmp["max_abs_value"]
+        ok = torch.equal(got[:, col0:col0 + w], c) and cmp["rel_frobenius"] <= 1e-3 and \
+            cmp["max_abs_diff"] <= tol
         out["gathered"] = {"ms_per_step": gms, "value": 2.0 * m * n * k / (gms * 1e-3) / 1e12,
                            "unit": "TFLOP/s",
                            "parity_ok_on_every_rank": all_max(0.0 if ok else 1.0) == 0.0,
-                           "checked": "own block and the next rank's block of the assembled C, bit "
-                                      "for bit against the same GEMM run locally"}
+                           "neighbour_block_rel_frobenius": all_max(cmp["rel_frobenius"]),
+                           "neighbour_block_max_abs_diff": all_max(cmp["max_abs_diff"]),
+                           "checked": "own block of the assembled C bit for bit against the local "
+                                      "c_shard; the next rank's block against the same GEMM run here "
+                                      "in one piece (rel. Frobenius <= 1e-3, max error <= "
+                                      "2e-2*sqrt(K/4096)*max|C|; the row panels of the gathered form "
+                                      "may split k differently, so the last bits can differ)"}
         del got, ref
         comm.free_shared(full_ptr)
     return out

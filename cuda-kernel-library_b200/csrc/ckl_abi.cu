@@ -284,6 +284,11 @@ Schedule make_schedule(int m, int n, int k, int mode, int max_units, int want_sk
     // so their groups are twice as high when there are columns enough (measured, 8192^3:
     // 1599 vs 1592 TFLOP/s; 6144^3: 1550 vs 1538).
     s.group_m = mode == kModeSingle ? 16 : (mode == kModePairWide && s.tiles_n >= 8) ? 16 : 8;
+#ifdef CKL_EXP
+    if (const char* g = std::getenv("CKL_GROUP_M")) {
+        s.group_m = std::max(1, std::atoi(g));
+    }
+#endif
     const int tiles = s.tiles_m * s.tiles_n;
     s.units = std::max(1, std::min(max_units, tiles));
     s.dp_tiles = tiles;

@@ -633,10 +633,8 @@ int ckl_gemm_gathered(ckl_comm* comm, int ab_dtype, const void* a, const void* b
     }
     // Row panels: the copy of panel i to every rank runs on s_coll while `stream` multiplies
     // panel i+1.  CKL_GATHER_PANELS overrides the count (1..8).
-    static const int forced_panels = [] {
-        const char* v = std::getenv("CKL_GATHER_PANELS");
-        return v != nullptr ? std::max(1, std::min(kMaxPanels, std::atoi(v))) : 0;
-    }();
+    const char* forced = std::getenv("CKL_GATHER_PANELS");
+    const int forced_panels = forced != nullptr ? std::max(1, std::min(kMaxPanels, std::atoi(forced))) : 0;
     int panels = forced_panels > 0 ? forced_panels : std::max(1, std::min(4, m / 2048));
     if (comm->world == 1) {
         panels = 1;

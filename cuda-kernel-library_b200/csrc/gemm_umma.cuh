@@ -80,6 +80,14 @@ struct GemmParams {
 #define CKL_STAGES_WIDE 3
 #endif
 
+// L2 eviction priority of the operand loads (ptx::kL2EvictNormal / First / Last).
+#ifndef CKL_HINT_A
+#define CKL_HINT_A ptx::kL2EvictNormal
+#endif
+#ifndef CKL_HINT_B
+#define CKL_HINT_B ptx::kL2EvictNormal
+#endif
+
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
 enum StatusCode : unsigned int {
@@ -495,7 +503,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // TMA producer.
             SegmentCursor cur = make_cursor(sched, unit);
             Segment seg;
-            constexpr uint64_t hint_a = ptx::kL2EvictNormal, hint_b = ptx::kL2EvictNormal;
+            constexpr uint64_t hint_a = CKL_HINT_A, hint_b = CKL_HINT_B;
             uint32_t it = 0;       // k blocks issued so far
             int stage = 0;         // it % kStages
             uint32_t phase = 0;    // (it / kStages) & 1

@@ -10,9 +10,13 @@
 //   dtype  : fp16 | bf16 (FP32 C, as the reference measures) or fp16_c16 | bf16_c16;
 //            fp32 with variant sgemm = the CUDA-core kernel behind the reference's FP32 rungs
 //     bench_all trsm blocked fp32 <m> <n> 0 [commit]   (the reference's trsm family, line 132-170)
+//     bench_all cpu reference fp32 <m> <n> <k> [commit]   the CPU GEMM of ckl/reference.hpp
+//            (the reference's include/ckl/reference.hpp:29-46: one thread, double accumulate)
+//            timed once on the host: the CPU baseline column of the sweep; no GPU is touched
 // Protocol: seeds 11 and 22, alpha 1, beta 0, 5 warm-ups, 20 timed launches, median.
 // The baseline column is the reference's cuBLAS wrapper when oracle/_ref holds its build.
 
+#include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <string>
@@ -20,6 +24,7 @@
 #include "ckl/device_buffer.hpp"
 #include "ckl/event_timer.hpp"
 #include "ckl/gemm.hpp"
+#include "ckl/reference.hpp"
 #include "harness.hpp"
 
 namespace {
@@ -154,13 +159,31 @@ Result run_trsm(int m, int n, const std::string& root) {
 
 int main(int argc, char** argv) {
     const std::string family = argc > 1 ? argv[1] : "";
-    if (argc < 7 || (family != "gemm" && family != "trsm")) {
-        std::fprintf(stderr, "usage: %s gemm|trsm <variant> <dtype> <m> <n> <k> [commit]\n", argv[0]);
+    if (argc < 7 || (family != "gemm" && family != "trsm" && family != "cpu")) {
+        std::fprintf(stderr, "usage: %s gemm|trsm|cpu <variant> <dtype> <m> <n> <k> [commit]\n", argv[0]);
         return 2;
     }
     const std::string variant = argv[2], dtype = argv[3];
     const int m = std::atoi(argv[4]), n = std::atoi(argv[5]), k = std::atoi(argv[6]);
     const std::string commit = argc > 7 ? argv[7] : "unknown";
+    if (family == "cpu") {
+        if (variant != "reference" || dtype != "fp32" || m <= 0 || n <= 0 || k <= 0) {
+            std::fprintf(stderr, "cpu family: bench_all cpu reference fp32 <m> <n> <k>\n");
+            return 3;
+        }
+        const auto ha = ckl::random_matrix(m, k, 11);
+        const auto hb = ckl::random_matrix(k, n, 22);
+        const std::vector<float> hc(static_cast<size_t>(m) * n, 0.0f);
+        const auto t0 = std::chrono::steady_clock::now();
+        const auto ref = ckl::gemm_reference(ha, hb, hc, m, n, k, 1.0f, 0.0f);
+        const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        std::printf("{\"family\":\"cpu\",\"variant\":\"reference\",\"dtype\":\"fp32\",\"m\":%d,\"n\":%d,"
+                    "\"k\":%d,\"gpus\":0,\"median_ms\":%.6f,\"gflops\":%.4f,\"cpu_cores\":1,"
+                    "\"checksum\":%.6e,\"commit\":\"%s\"}\n",
+                    m, n, k, ms, ckl::gemm_gflops(m, n, k, ms), ref[0] + ref[ref.size() - 1],
+                    commit.c_str());
+        return 0;
+    }
     const char* root_env = std::getenv("CKL_REPO_ROOT");
     const std::string root = root_env ? root_env : ".";
     const bool fp32 = dtype == "fp32";

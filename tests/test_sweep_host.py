@@ -20,15 +20,27 @@ def _load():
 
 def test_sweep_resumes_and_forces(tmp_path):
     sw = _load()
-    calls = []
+    calls, cpu_calls = [], []
 
     def fake_run(cmd, **kwargs):
-        _, family, variant, dtype, m, n, k, commit = cmd
+        if "torch.distributed.run" in cmd:            # an N-sharded row: one torchrun job
+            gpus = int([c for c in cmd if c.startswith("--nproc-per-node=")][0].split("=")[1])
+            assert cmd[cmd.index("--master-addr") + 1] == "127.0.0.1"
+            assert cmd[-7].endswith("sharded_row.py")
+            variant, dtype, m, n, k, commit = cmd[-6:]
+            family = "gemm"
+        else:
+            _, family, variant, dtype, m, n, k, commit = cmd
+            gpus = 1
+        if family == "cpu":                            # the CPU baseline, once per sweep
+            cpu_calls.append(tuple(cmd[1:]))
+            row = {"family": "cpu", "gflops": 2.5, "cpu_cores": 1}
+            return types.SimpleNamespace(returncode=0, stdout=json.dumps(row) + "\n", stderr="")
         calls.append(tuple(cmd[1:]))
         if variant == "umma_1cta" and m == "1024":      # one configuration fails
             return types.SimpleNamespace(returncode=3, stdout="", stderr="boom")
         row = {"family": family, "variant": variant, "dtype": dtype, "m": int(m), "n": int(n),
-               "k": int(k), "gpus": 1, "median_ms": 1.0, "iqr_ms": 0.0, "gflops": 1.0,
+               "k": int(k), "gpus": gpus, "median_ms": 1.0, "iqr_ms": 0.0, "gflops": 1.0,
                "tflops": 0.001, "commit": commit}
         return types.SimpleNamespace(returncode=0, stdout=json.dumps(row) + "\n", stderr="")
 
@@ -46,6 +58,19 @@ def test_sweep_resumes_and_forces(tmp_path):
     assert (ran, skipped) == (total - 1, 0)
     header = open(tmp_path / "summary.csv").readline().strip().split(",")
     assert header[:7] == ["family", "variant", "dtype", "m", "n", "k", "gpus"]
+    assert {"pct_peak_measured", "cpu_baseline_gflops", "cpu_cores"} <= set(header)
+    # the CPU baseline is timed once per sweep that runs anything and lands in every row
+    assert all(c[:3] == ("cpu", "reference", "fp32") for c in cpu_calls) and len(cpu_calls) == 3
+    rows = [json.loads(line) for line in open(tmp_path / "sweep.jsonl")]
+    assert all(r["cpu_baseline_gflops"] == 2.5 and r["cpu_cores"] == 1 for r in rows)
+    # GPU counts above one add the N-sharded rows, keyed by `gpus`, one torchrun job each
+    multi = [c for c in sw.matrix(quick=True, gpu_counts=[2, 8]) if c["gpus"] > 1]
+    assert [(c["gpus"], c["m"]) for c in multi] == [(2, 8192), (8, 8192)]
+    calls.clear()
+    ran, skipped = sw.sweep(str(tmp_path), quick=True, commit="abc", runner=fake_run, gpu_counts=[2])
+    assert ran == 1 and skipped == total - 1           # (the failing single-GPU one is tried again)
+    rows = [json.loads(line) for line in open(tmp_path / "sweep.jsonl")]
+    assert sum(1 for r in rows if r["gpus"] == 2 and r["commit"] == "abc") == 1
 
 
 def test_ncu_round_commands(tmp_path, monkeypatch):
@@ -85,3 +110,16 @@ def test_ncu_round_commands(tmp_path, monkeypatch):
     assert (tmp_path / "r1" / "umma_2cta_wide_8192.txt").read_text().strip() == "details page"
     meta = (tmp_path / "r1" / "round_meta.txt").read_text()
     assert "round: r1" in meta and "commit:" in meta
+
+
+def test_bench_all_cpu_baseline_row():
+    """`bench_all cpu reference fp32 m n k` times the CPU GEMM of ckl/reference.hpp (the
+    reference's include/ckl/reference.hpp:29-46) on the host; no GPU is needed."""
+    import subprocess
+    from conftest import tool_binary
+    out = subprocess.run([tool_binary("bench_all"), "cpu", "reference", "fp32", "96", "64", "80", "t"],
+                         capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr
+    row = json.loads(out.stdout.strip())
+    assert (row["family"], row["variant"], row["m"], row["n"], row["k"]) == ("cpu", "reference", 96, 64, 80)
+    assert row["cpu_cores"] == 1 and row["gflops"] > 0 and row["gpus"] == 0
