@@ -237,6 +237,16 @@ def last_plan() -> Plan:
     return plan
 
 
+_lib.ckl_test_arm_wait_fault.argtypes = [_i, ctypes.c_ulonglong]
+_lib.ckl_test_arm_wait_fault.restype = ctypes.c_int
+
+
+def arm_wait_fault(kind: int, wait_limit_ns: int = 0) -> None:
+    """Test hook: one bounded wait of this thread's next tensor-core launch runs out
+    (kind 1: a pipeline stage that never completes; kind 2: a stream-K flag nobody sets)."""
+    _check(_lib.ckl_test_arm_wait_fault(kind, wait_limit_ns))
+
+
 def debug_counter(name: str) -> int:
     return int(_lib.ckl_debug_counter(name.encode()))
 

@@ -123,6 +123,12 @@ struct DeviceCtx {
 };
 
 std::atomic<unsigned long long> g_tensor_map_encodes{0};
+// Armed by ckl_test_arm_wait_fault for the calling thread's next tensor-core launch.
+struct WaitFault {
+    int kind = 0;
+    unsigned long long limit_ns = 0;
+};
+thread_local WaitFault g_wait_fault;
 thread_local ckl_plan g_last_plan = {};
 
 std::mutex g_ctx_mu;
@@ -737,6 +743,14 @@ int gemm_impl(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, 
     p.idesc = ptx::make_idesc_f16(ab_dtype == CKL_F16 ? 0u : 1u, 0u, 1u, plan.pair ? 256u : 128u,
                                   256u);
     p.sched = plan.sched;
+    p.wait_limit_ns = kWaitLimitNs;
+    const WaitFault fault = g_wait_fault;
+    g_wait_fault = WaitFault{};  // one launch only
+    if (fault.kind != 0) {
+        p.wait_limit_ns = fault.limit_ns != 0 ? fault.limit_ns : kWaitLimitNs;
+        p.overstate_first_stage = fault.kind == 1 ? 1 : 0;
+        p.sk_flag_skew = fault.kind == 2 ? 1u : 0u;
+    }
     if (plan.workspace_bytes > 0) {
         unsigned int* flags = nullptr;
         unsigned int epoch = 0;
@@ -1084,6 +1098,15 @@ int ckl_last_plan(ckl_plan* out) {
         return fail(CKL_ERR_INVALID_ARG, "ckl_last_plan: out is null");
     }
     *out = g_last_plan;
+    return CKL_OK;
+}
+
+int ckl_test_arm_wait_fault(int kind, unsigned long long wait_limit_ns) {
+    if (kind < 0 || kind > 2) {
+        return fail(CKL_ERR_INVALID_ARG, "ckl_test_arm_wait_fault: kind must be 0, 1 or 2");
+    }
+    g_wait_fault.kind = kind;
+    g_wait_fault.limit_ns = wait_limit_ns;
     return CKL_OK;
 }
 

@@ -67,6 +67,14 @@ struct GemmParams {
     int epi_mode;
     uint32_t idesc;
     Schedule sched;
+    // Limit of every bounded wait in nanoseconds; 0 means kWaitLimitNs.
+    unsigned long long wait_limit_ns;
+    // Test hooks, both 0 in every ordinary launch.  sk_flag_skew is added to the flag value the
+    // owner of a split tile waits for, so a non-zero skew makes that wait run out;
+    // overstate_first_stage makes unit 0's producer announce 16 bytes more than it loads for
+    // its first stage, so that stage never completes and the MMA warp's wait runs out.
+    unsigned int sk_flag_skew;
+    int overstate_first_stage;
 };
 
 // Depth of the shared-memory ring (48 KB per stage for one CTA, 64 KB per CTA of a pair).
@@ -147,6 +155,7 @@ struct Control {
     unsigned int* status;
     bool pair;
     uint32_t peer_rank;
+    unsigned long long limit_ns;  // every bounded wait gives up after this long
 };
 
 __device__ __forceinline__ void raise_abort(const Control& ctl, unsigned int role,
@@ -184,7 +193,7 @@ __device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, cons
             const unsigned long long now = ptx::global_timer_ns();
             if (t0 == 0) {
                 t0 = now;
-            } else if (now - t0 > kWaitLimitNs) {
+            } else if (now - t0 > ctl.limit_ns) {
                 raise_abort(ctl, role, detail_word);
                 return false;
             }
@@ -209,7 +218,7 @@ __device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int
             const unsigned long long now = ptx::global_timer_ns();
             if (t0 == 0) {
                 t0 = now;
-            } else if (now - t0 > kWaitLimitNs) {
+            } else if (now - t0 > ctl.limit_ns) {
                 raise_abort(ctl, role, detail_word);
                 return false;
             }
@@ -437,6 +446,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ctl.abort_flag_smem = tmem_slot + 4u;
     ctl.status = p.status;
     ctl.pair = kPair;
+    ctl.limit_ns = p.wait_limit_ns != 0 ? p.wait_limit_ns : kWaitLimitNs;
 
     const int warp = static_cast<int>(threadIdx.x >> 5);
     const uint32_t lane = ptx::lane_id();
@@ -526,13 +536,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const uint32_t b_dst = a_dst + Cfg::kABytes;
                     {
                         uint32_t bar = full_bar(stage);
+                        // (test hook: unit 0 may overstate its first stage, see GemmParams)
+                        const uint32_t tx = Cfg::kTxBytes +
+                                            ((p.overstate_first_stage != 0 && it == 0 && unit == 0) ? 16u : 0u);
                         if constexpr (kPair) {
                             if (leader) {
-                                ptx::mbar_arrive_expect_tx(bar, Cfg::kTxBytes);
+                                ptx::mbar_arrive_expect_tx(bar, tx);
                             }
                             bar = ptx::map_to_cta(bar, 0);  // both CTAs credit the leader's barrier
                         } else {
-                            ptx::mbar_arrive_expect_tx(bar, Cfg::kTxBytes);
+                            ptx::mbar_arrive_expect_tx(bar, tx);
                         }
 #pragma unroll
                         for (int sub = 0; sub < Cfg::kKSub; ++sub) {
@@ -877,7 +890,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     for (int v = 0; v < peers && got; ++v) {
                         const unsigned int* flag =
                             p.sk_flags + static_cast<size_t>(2 * (unit + 1 + v)) * 16 + group * 2 + half;
-                        got = detail::wait_flag(flag, p.sk_epoch, ctl, kRoleEpilogue,
+                        got = detail::wait_flag(flag, p.sk_epoch + p.sk_flag_skew, ctl, kRoleEpilogue,
                                                 0x50000000u | static_cast<unsigned int>(unit + 1 + v))
                                   ? 1
                                   : 0;
@@ -890,7 +903,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 for (int v = 0; v < peers; ++v) {
                     const unsigned int* flag =
                         p.sk_flags + static_cast<size_t>(2 * (unit + 1 + v)) * 16 + group * 2 + half;
-                    for (int i = 0; i < 1024 && ptx::ld_acquire_gpu(flag) != p.sk_epoch; ++i) {
+                    for (int i = 0; i < 1024 && ptx::ld_acquire_gpu(flag) != p.sk_epoch + p.sk_flag_skew; ++i) {
                     }
                 }
             }

@@ -313,6 +313,20 @@ int ckl_noalloc_device_status(unsigned int* info);
 const char* ckl_noalloc_last_error(void);
 size_t ckl_noalloc_scratch_bytes(void);
 
+/* Test hook for the bounded waits (no fault is raised, nothing traps, no wait exceeds the
+ * limit given here): makes ONE wait of the calling thread's next tensor-core launch run out.
+ *   kind 1: the TMA producer of the first CTA announces 16 bytes more than it loads for its
+ *           first pipeline stage, so that stage's barrier never completes and the MMA warp's
+ *           wait gives up;
+ *   kind 2: the owner of a split tile (fused stream-K launches only) waits for a flag value
+ *           that no CTA publishes.
+ * The waiting role records (code, block, role, detail) in the device status word, every role
+ * of the CTA leaves its loop, copies and MMAs in flight are drained, tensor memory is freed
+ * and the kernel returns; C of that launch is incomplete, ckl_device_status() then returns
+ * CKL_ERR_DEVICE, and the next launch runs normally.  wait_limit_ns replaces the 2 s limit
+ * for that launch (0 keeps it).  kind 0 disarms. */
+int ckl_test_arm_wait_fault(int kind, unsigned long long wait_limit_ns);
+
 /* Counters for tests: "tensor_map_encodes" = TMA descriptors encoded by this process so far
  * (descriptors are cached per device, keyed by address, shape, pitch, type and box, so a
  * repeated call encodes none).  Unknown names give ~0. */
