@@ -16,8 +16,10 @@
 // On this hardware every FP16 "rung" of the reference ladder is the same
 // TMA + tcgen05 kernel and every FP32 rung the same CUDA-core kernel; the
 // distinct names survive only for source compatibility.  Additions over the reference are grouped at the end:
-// 16-bit C, explicit leading dimensions, kernel selection.
+// 16-bit C, explicit leading dimensions, kernel selection, and the N-sharded forms for several
+// GPUs of one box (the reference is single-GPU).
 
+#include <cstddef>
 #include <stdexcept>
 #include <string>
 
@@ -165,6 +167,62 @@ template <typename InT, typename OutT>
 inline void gemm_tensor(const InT* a, const InT* b, OutT* c, int m, int n, int k, float alpha,
                         float beta, cudaStream_t stream = nullptr) {
     gemm_tensor(a, b, c, m, n, k, k, n, n, alpha, beta, stream, CKL_ALGO_AUTO);
+}
+
+// ---- several GPUs of one box: one rank (process or thread) per GPU ----------------
+// Rank r of `world` owns the column block ckl_column_shard(n, world, r, 8, ...) of B and C;
+// A is replicated.  The communicator is made once per rank with its device current:
+// rank 0 calls ckl_comm_get_unique_id and hands the 128 bytes to the others, then every rank
+// constructs a ShardedComm.  See ckl_gemm.h for the contracts of the calls wrapped here.
+
+class ShardedComm {
+public:
+    ShardedComm(int world, int rank, const void* unique_id) {
+        detail::throw_on_error(ckl_comm_init(&comm_, world, rank, unique_id), "ShardedComm");
+    }
+    ~ShardedComm() { ckl_comm_destroy(comm_); }
+    ShardedComm(const ShardedComm&) = delete;
+    ShardedComm& operator=(const ShardedComm&) = delete;
+    ckl_comm* get() const { return comm_; }
+    int world() const { return ckl_comm_world(comm_); }
+    int rank() const { return ckl_comm_rank(comm_); }
+
+    // A buffer that exists on every rank with every copy mapped everywhere (collective).
+    void* alloc_shared(std::size_t bytes) {
+        void* p = nullptr;
+        detail::throw_on_error(ckl_comm_alloc_shared(comm_, bytes, &p), "alloc_shared");
+        return p;
+    }
+    void free_shared(void* p) { detail::throw_on_error(ckl_comm_free_shared(comm_, p), "free_shared"); }
+
+private:
+    ckl_comm* comm_ = nullptr;
+};
+
+// Host buffers in, host buffers out: a_rows holds the rows of A that
+// ckl_plan_host_sharded(m, world, rank) assigns to this rank, b_shard and c_shard its packed
+// column blocks.  Collective.
+template <typename InT, typename OutT>
+inline void gemm_tensor_host_sharded(ShardedComm& comm, const InT* a_rows, const InT* b_shard,
+                                     OutT* c_shard, int m, int n_shard, int k, float alpha,
+                                     float beta) {
+    detail::throw_on_error(
+        ckl_gemm_host_sharded(comm.get(), detail::dtype_of(a_rows), a_rows, b_shard, c_shard,
+                              detail::dtype_of(c_shard), m, n_shard, k, alpha, beta),
+        "gemm_tensor_host_sharded");
+}
+
+// Device buffers; every rank ends with the whole row-major m x n matrix in c_full (a buffer
+// from ShardedComm::alloc_shared).  c_shard is the rank's packed m x width block.  Collective
+// and stream-ordered.
+template <typename InT, typename OutT>
+inline void gemm_tensor_gathered(ShardedComm& comm, const InT* a, const InT* b_shard, OutT* c_shard,
+                                 OutT* c_full, int m, int n, int k, int lda, int ldb, float alpha,
+                                 float beta, cudaStream_t stream = nullptr) {
+    detail::throw_on_error(
+        ckl_gemm_gathered(comm.get(), detail::dtype_of(a), a, b_shard, c_shard, c_full,
+                          detail::dtype_of(c_shard), m, n, k, lda, ldb, alpha, beta, stream),
+        "gemm_tensor_gathered");
 }
 
 }  // namespace ckl
