@@ -45,7 +45,7 @@ class Plan(ctypes.Structure):
         ("k_blocks", ctypes.c_int), ("grid", ctypes.c_int), ("units", ctypes.c_int),
         ("group_m", ctypes.c_int), ("dp_tiles", ctypes.c_int),
         ("sk_tiles", ctypes.c_int), ("sk_units", ctypes.c_int), ("sk_iters", ctypes.c_longlong),
-        ("workspace_bytes", ctypes.c_size_t),
+        ("workspace_bytes", ctypes.c_size_t), ("repack", ctypes.c_int),
     ]
 
 

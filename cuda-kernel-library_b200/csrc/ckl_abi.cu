@@ -106,6 +106,7 @@ struct DeviceCtx {
     EncodeTiledFn encode = nullptr;
     unsigned int* status = nullptr;            // 4 words on the device
     std::map<cudaStream_t, Staging> workspace; // stream-K partial slots, one per stream
+    std::map<cudaStream_t, Staging> repack;    // aligned copies of operands TMA cannot describe
     Staging host_a, host_b, host_c;            // device staging for ckl_gemm_host
     cudaStream_t host_stream = nullptr;        // ckl_gemm_host: compute
     cudaStream_t host_in = nullptr;            // ckl_gemm_host: host -> device copies
@@ -249,6 +250,7 @@ struct Plan {
     int algo = CKL_ALGO_SIMT;
     int mode = kModeSingle;
     bool pair = false;
+    bool repack = false;  // AUTO only: A and/or B are first copied to an aligned pitch
     int tile_m = 64, tile_n = 64, tile_k = 16;
     int grid = 0;
     Schedule sched = {};
@@ -272,7 +274,11 @@ void export_plan(const Plan& plan, ckl_plan* out) {
     out->sk_units = plan.sched.sk_tiles > 0 ? plan.sched.units : 0;
     out->sk_iters = plan.sched.sk_iters;
     out->workspace_bytes = plan.workspace_bytes;
+    out->repack = plan.repack ? 1 : 0;
 }
+
+// 2^28 multiply-adds (645^3): below this the general kernel's one launch wins.
+constexpr long long kRepackMinMacs = 1LL << 28;
 
 bool tma_legal(int k, int lda, int ldb, size_t a_align, size_t b_align) {
     return k > 0 && lda % 8 == 0 && ldb % 8 == 0 && a_align % 16 == 0 && b_align % 16 == 0;
@@ -351,8 +357,18 @@ Schedule make_schedule(int m, int n, int k, int mode, int max_units, int want_sk
 // C is also read), which sets how long the exposed epilogue of the 256x512 tile is.
 int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_align, int algo,
               int sm_count, int max_pairs, int c_traffic, Plan* plan) {
-    const bool legal = tma_legal(k, lda, ldb, a_align, b_align);
+    bool legal = tma_legal(k, lda, ldb, a_align, b_align);
     int resolved = algo;
+    plan->repack = false;
+    if (algo == CKL_ALGO_AUTO && !legal && k > 0 &&
+        static_cast<long long>(m) * n * static_cast<long long>(k) >= kRepackMinMacs) {
+        // Operands TMA cannot describe (base not 16-byte aligned, pitch not a multiple of 8
+        // elements): from this size on two copy passes to an aligned pitch and the tensor-core
+        // kernel beat the CUDA-core kernel by a wide margin.  Smaller problems keep the
+        // general kernel, whose single launch is cheaper than three.
+        legal = true;
+        plan->repack = true;
+    }
     if (algo == CKL_ALGO_AUTO) {
         // Measured on B200: once there is at least one 256x256 tile per CTA pair the pair
         // kernel wins (half the B traffic per SM); below that the 128x256 single-CTA tiles
@@ -698,6 +714,53 @@ int gemm_impl(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, 
                                             beta, epi, stream)
                    : launch_simt_in<__nv_bfloat16>(c_dtype, a, b, c, bias, m, n, k, lda, ldb, ldc,
                                                    alpha, beta, epi, stream);
+    }
+
+    if (plan.repack) {
+        // Aligned copies of whichever operand needs one, in this stream's scratch (grown on
+        // demand, reused by later calls on the stream: stream order keeps a later copy from
+        // overwriting what an earlier GEMM still reads).
+        const bool fix_a = reinterpret_cast<uintptr_t>(a) % 16 != 0 || lda % 8 != 0;
+        const bool fix_b = reinterpret_cast<uintptr_t>(b) % 16 != 0 || ldb % 8 != 0;
+        const size_t pitch_a = (static_cast<size_t>(k) + 63) / 64 * 64;   // 128-byte rows
+        const size_t pitch_b = (static_cast<size_t>(n) + 63) / 64 * 64;
+        const size_t bytes_a = fix_a ? static_cast<size_t>(m) * pitch_a * 2 : 0;
+        const size_t bytes_b = fix_b ? static_cast<size_t>(k) * pitch_b * 2 : 0;
+        unsigned char* scratch = nullptr;
+        {
+            std::lock_guard<std::mutex> lock(ctx->mu);
+            Staging& buf = ctx->repack[stream];
+            if (buf.bytes < bytes_a + bytes_b) {
+                if (buf.ptr != nullptr) {
+                    CKL_TRY_CUDA(cudaStreamSynchronize(stream));
+                    CKL_TRY_CUDA(cudaFree(buf.ptr));
+                    buf.ptr = nullptr;
+                    buf.bytes = 0;
+                }
+                CKL_TRY_CUDA(cudaMalloc(&buf.ptr, bytes_a + bytes_b));
+                buf.bytes = bytes_a + bytes_b;
+            }
+            scratch = static_cast<unsigned char*>(buf.ptr);
+        }
+        auto copy = [&](void* dst, const void* src, int rows, int cols, int src_ld, size_t dst_ld) {
+            const size_t groups = (static_cast<size_t>(cols) + 7) / 8 * static_cast<size_t>(rows);
+            const int blocks = static_cast<int>(std::min<size_t>((groups + 255) / 256,
+                                                                 static_cast<size_t>(ctx->sm_count) * 16));
+            repack_rows_kernel<<<blocks, 256, 0, stream>>>(static_cast<uint16_t*>(dst),
+                                                           static_cast<const uint16_t*>(src), rows, cols,
+                                                           static_cast<size_t>(src_ld), dst_ld);
+        };
+        if (fix_a) {
+            copy(scratch, a, m, k, lda, pitch_a);
+            a = scratch;
+            lda = static_cast<int>(pitch_a);
+        }
+        if (fix_b) {
+            copy(scratch + bytes_a, b, k, n, ldb, pitch_b);
+            b = scratch + bytes_a;
+            ldb = static_cast<int>(pitch_b);
+        }
+        CKL_TRY_CUDA(cudaGetLastError());
     }
 
     CUtensorMap ta, tb;
@@ -1285,6 +1348,9 @@ void ckl_shutdown(void) {
         }
         cudaDeviceSynchronize();
         for (auto& w : ctx->workspace) {
+            cudaFree(w.second.ptr);
+        }
+        for (auto& w : ctx->repack) {
             cudaFree(w.second.ptr);
         }
         cudaFree(ctx->host_a.ptr);

@@ -76,9 +76,13 @@ int ckl_gemm_bf16(const void* a, const void* b, void* c, int c_dtype, int m, int
 /* Same computation with the input type and the kernel chosen by argument.
  * Forcing a tensor-core algo on a shape it cannot take (A or B not 16-byte
  * aligned, lda or ldb not a multiple of 8 elements, k <= 0) returns
- * CKL_ERR_UNSUPPORTED; CKL_ALGO_AUTO routes such shapes to CKL_ALGO_SIMT the
+ * CKL_ERR_UNSUPPORTED.  CKL_ALGO_AUTO routes such shapes to CKL_ALGO_SIMT the
  * way the reference routes them to its scalar kernel
- * (include/ckl/detail/wmma_gemm.cuh:148-158). */
+ * (include/ckl/detail/wmma_gemm.cuh:148-158) while they are small; from
+ * m*n*k = 2^28 on it copies the offending operand(s) into a per-stream scratch
+ * buffer with an aligned pitch (one copy kernel each, scratch allocated on first
+ * use: make that call outside stream capture) and runs the tensor-core kernel
+ * on the copies, so an odd leading dimension no longer costs the tensor cores. */
 int ckl_gemm_ex(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, int m, int n,
                 int k, int lda, int ldb, int ldc, float alpha, float beta, int algo,
                 ckl_stream_t stream);
@@ -147,6 +151,7 @@ typedef struct ckl_plan {
     int sk_units;       /* CTAs (or pairs) sharing the split tiles */
     long long sk_iters; /* total k-block iterations in the split region */
     size_t workspace_bytes;
+    int repack;         /* 1: A and/or B are first copied to a 128-byte-aligned pitch (below) */
 } ckl_plan;
 int ckl_plan_gemm(int m, int n, int k, int lda, int ldb, int ldc, int a_align, int b_align,
                   int algo, int sm_count, ckl_plan* out);

@@ -164,6 +164,24 @@ def test_plan_sees_the_output_type_and_the_pair_count(ckl):
     assert ckl.debug_counter("tensor_map_encodes") == 0      # nothing was launched here
 
 
+def test_large_unaligned_shapes_are_repacked_onto_the_tensor_path(ckl):
+    """An odd leading dimension or base keeps a SMALL problem on the general kernel (one launch);
+    from m*n*k = 2^28 on AUTO copies the operand to an aligned pitch and takes the tensor-core
+    kernel.  Forcing a tensor-core kernel on such a shape is still refused."""
+    small = ckl.plan_gemm(129, 257, 193)
+    assert small.algo == ckl.ALGO_SIMT and small.repack == 0
+    big = ckl.plan_gemm(4097, 4097, 4097)
+    assert big.algo != ckl.ALGO_SIMT and big.repack == 1 and big.tile_m in (128, 256)
+    assert ckl.plan_gemm(4096, 4096, 4096, a_align=2).repack == 1          # base off by one element
+    assert ckl.plan_gemm(4096, 4096, 4096).repack == 0
+    edge = ckl.plan_gemm(1000, 1001, 1003)
+    assert edge.repack == 1 and edge.algo != ckl.ALGO_SIMT
+    assert ckl.plan_gemm(640, 641, 643).algo == ckl.ALGO_SIMT              # 2.6e8 < 2^28
+    with pytest.raises(ckl.CklError) as e:
+        ckl.plan_gemm(4097, 4097, 4097, algo=ckl.ALGO_UMMA_2CTA)
+    assert e.value.status == ckl.ERR_UNSUPPORTED
+
+
 SHAPES = [(128, 256, 64), (256, 256, 256), (4000, 3000, 5000), (1024, 1024, 32768),
           (8192, 8192, 8192), (8192, 1024, 8192), (16384, 1792, 4096), (200, 264, 72),
           (2304, 4096, 1024), (1000, 776, 520), (128, 256, 6400), (100000, 256, 64)]

@@ -448,6 +448,46 @@ def test_assemble_column_blocks(env):
         assert torch.equal(dst, src.permute(1, 0, 2).reshape(m, parts * width))
 
 
+@pytest.mark.parametrize("shape", [(1000, 1001, 1003), (1024, 1001, 1024), (1000, 1024, 1003),
+                                   (2049, 2055, 517)], ids=lambda s: "x".join(map(str, s)))
+def test_unaligned_operands_are_repacked_and_match_the_oracle(env, shape):
+    """Leading dimensions that are not multiples of 8 (and, in the last pass, bases that are not
+    16-byte aligned) on problems large enough for the repack path: the tensor-core kernel runs
+    on aligned copies, C keeps its own odd pitch, and the result meets the oracle."""
+    m, n, k = shape
+    ckl, orc = env.ckl, env.orc
+    fa = orc.random_matrix(m, k, 0x1111 + m)
+    fb = orc.random_matrix(k, n, 0x2222 + n)
+    fc = orc.random_matrix(m, n, 0x9ABC + k)
+    for dt, cdt, alpha, beta in [(ckl.F16, ckl.F32, 1.0, 0.0), (ckl.BF16, ckl.BF16, 1.0, 0.5)]:
+        da, ra = env.narrow_dev(fa, dt)
+        db, rb = env.narrow_dev(fb, dt)
+        if cdt == ckl.F32:
+            dc, rc = torch.from_numpy(fc).cuda(), fc
+        else:
+            dc, rc = env.narrow_dev(fc, cdt)
+        ckl.gemm_ex(dt, da, db, dc, cdt, m, n, k, k, n, n, alpha, beta)
+        torch.cuda.synchronize()
+        plan = ckl.last_plan()
+        assert plan.repack == 1 and plan.algo != ckl.ALGO_SIMT
+        ref, _ = orc.gemm_reference_mt(ra, rb, rc, alpha, beta)
+        env.gate(env.c_to_host(dc, cdt), ref, k, cdt, f"repack {m}x{n}x{k} in={dt} out={cdt}")
+    # the same through bases that sit one element past a 16-byte boundary
+    dt = ckl.F16
+    da, ra = env.narrow_dev(fa, dt)
+    db, rb = env.narrow_dev(fb, dt)
+    pad_a = torch.zeros(m * k + 1, dtype=torch.float16, device="cuda")
+    pad_b = torch.zeros(k * n + 1, dtype=torch.float16, device="cuda")
+    pad_a[1:].copy_(da.reshape(-1))
+    pad_b[1:].copy_(db.reshape(-1))
+    dc = torch.zeros(m, n, device="cuda")
+    ckl.gemm_ex(dt, pad_a.data_ptr() + 2, pad_b.data_ptr() + 2, dc, ckl.F32, m, n, k, k, n, n, 1.0, 0.0)
+    torch.cuda.synchronize()
+    assert ckl.last_plan().repack == 1
+    ref, _ = orc.gemm_reference_mt(ra, rb, None, 1.0, 0.0)
+    env.gate(dc.cpu().numpy(), ref, k, ckl.F32, f"repack, odd bases {m}x{n}x{k}")
+
+
 def test_descriptors_are_cached_and_the_plan_is_reported(env):
     """A repeated call encodes no TMA descriptor (they are cached per device by address, shape,
     pitch, type and box), a call on other buffers encodes its own, and ckl_last_plan reports
