@@ -256,7 +256,7 @@ int ckl_plan_host_sharded(int m, int world, int rank, ckl_host_shard_plan* out);
  * k x n_shard block and c_shard_host its m x n_shard block (both packed).  Each rank uploads
  * over its own link, the row panels of A are all-gathered over NVLink, and panel j is
  * multiplied and sent back while panel j+1 is still arriving.  Collective; returns when this
- * rank's block of C is in c_shard_host.  With world == 1 it is ckl_gemm_host. */
+ * rank's block of C is in c_shard_host.  With world == 1 it does what ckl_gemm_host does. */
 int ckl_gemm_host_sharded(ckl_comm* comm, int ab_dtype, const void* a_rows_host,
                           const void* b_shard_host, void* c_shard_host, int c_dtype, int m,
                           int n_shard, int k, float alpha, float beta);
