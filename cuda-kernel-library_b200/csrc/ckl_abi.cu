@@ -655,6 +655,17 @@ int launch_scale(void* c, const float* bias, int m, int n, int ldc, float beta, 
     return CKL_OK;
 }
 
+template <typename T, bool kDstAligned>
+void launch_copy_rows(const DeviceCtx* ctx, void* dst, const void* src, int rows, int cols, int src_ld,
+                      size_t dst_ld, cudaStream_t stream) {
+    constexpr size_t kPer = 16 / sizeof(T);
+    const size_t groups = (static_cast<size_t>(cols) + kPer - 1) / kPer * static_cast<size_t>(rows);
+    const int blocks = static_cast<int>(
+        std::max<size_t>(1, std::min<size_t>((groups + 255) / 256, static_cast<size_t>(ctx->sm_count) * 16)));
+    copy_rows_kernel<T, kDstAligned><<<blocks, 256, 0, stream>>>(
+        static_cast<T*>(dst), static_cast<const T*>(src), rows, cols, static_cast<size_t>(src_ld), dst_ld);
+}
+
 int gemm_impl(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, const float* bias,
               int m, int n, int k, int lda, int ldb, int ldc, float alpha, float beta, int epi,
               int algo, cudaStream_t stream) {
@@ -716,49 +727,69 @@ int gemm_impl(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, 
                                                    alpha, beta, epi, stream);
     }
 
-    if (plan.repack) {
-        // Aligned copies of whichever operand needs one, in this stream's scratch (grown on
-        // demand, reused by later calls on the stream: stream order keeps a later copy from
-        // overwriting what an earlier GEMM still reads).
+    // Operands TMA cannot describe travel through aligned copies in this stream's scratch
+    // (grown on demand, reused by later calls on the stream: stream order keeps a later copy
+    // from overwriting what an earlier GEMM still reads).  The same goes for a C whose base or
+    // pitch rules out 16-byte accesses on a large problem: the kernel writes an aligned copy
+    // through its TMA epilogue and one pass copies it out, instead of the register-store
+    // epilogue's 2-byte stores (C_in is copied in first when it is read).
+    const size_t csz = dtype_size(c_dtype);
+    const bool c_aligned =
+        reinterpret_cast<uintptr_t>(c) % 16 == 0 && (static_cast<size_t>(ldc) * csz) % 16 == 0;
+    const bool stage_c = algo == CKL_ALGO_AUTO && !c_aligned &&
+                         static_cast<long long>(m) * n * static_cast<long long>(k) >= kRepackMinMacs;
+    void* c_user = c;
+    const int ldc_user = ldc;
+    if (stage_c) {
+        g_last_plan.repack = 1;
+    }
+    if (plan.repack || stage_c) {
         const bool fix_a = reinterpret_cast<uintptr_t>(a) % 16 != 0 || lda % 8 != 0;
         const bool fix_b = reinterpret_cast<uintptr_t>(b) % 16 != 0 || ldb % 8 != 0;
         const size_t pitch_a = (static_cast<size_t>(k) + 63) / 64 * 64;   // 128-byte rows
         const size_t pitch_b = (static_cast<size_t>(n) + 63) / 64 * 64;
+        const size_t per_line = 128 / csz;
+        const size_t pitch_c = (static_cast<size_t>(n) + per_line - 1) / per_line * per_line;
         const size_t bytes_a = fix_a ? static_cast<size_t>(m) * pitch_a * 2 : 0;
         const size_t bytes_b = fix_b ? static_cast<size_t>(k) * pitch_b * 2 : 0;
+        const size_t bytes_c = stage_c ? static_cast<size_t>(m) * pitch_c * csz : 0;
         unsigned char* scratch = nullptr;
         {
             std::lock_guard<std::mutex> lock(ctx->mu);
             Staging& buf = ctx->repack[stream];
-            if (buf.bytes < bytes_a + bytes_b) {
+            if (buf.bytes < bytes_a + bytes_b + bytes_c) {
                 if (buf.ptr != nullptr) {
                     CKL_TRY_CUDA(cudaStreamSynchronize(stream));
                     CKL_TRY_CUDA(cudaFree(buf.ptr));
                     buf.ptr = nullptr;
                     buf.bytes = 0;
                 }
-                CKL_TRY_CUDA(cudaMalloc(&buf.ptr, bytes_a + bytes_b));
-                buf.bytes = bytes_a + bytes_b;
+                CKL_TRY_CUDA(cudaMalloc(&buf.ptr, bytes_a + bytes_b + bytes_c));
+                buf.bytes = bytes_a + bytes_b + bytes_c;
             }
             scratch = static_cast<unsigned char*>(buf.ptr);
         }
-        auto copy = [&](void* dst, const void* src, int rows, int cols, int src_ld, size_t dst_ld) {
-            const size_t groups = (static_cast<size_t>(cols) + 7) / 8 * static_cast<size_t>(rows);
-            const int blocks = static_cast<int>(std::min<size_t>((groups + 255) / 256,
-                                                                 static_cast<size_t>(ctx->sm_count) * 16));
-            repack_rows_kernel<<<blocks, 256, 0, stream>>>(static_cast<uint16_t*>(dst),
-                                                           static_cast<const uint16_t*>(src), rows, cols,
-                                                           static_cast<size_t>(src_ld), dst_ld);
-        };
         if (fix_a) {
-            copy(scratch, a, m, k, lda, pitch_a);
+            launch_copy_rows<uint16_t, true>(ctx, scratch, a, m, k, lda, pitch_a, stream);
             a = scratch;
             lda = static_cast<int>(pitch_a);
         }
         if (fix_b) {
-            copy(scratch + bytes_a, b, k, n, ldb, pitch_b);
+            launch_copy_rows<uint16_t, true>(ctx, scratch + bytes_a, b, k, n, ldb, pitch_b, stream);
             b = scratch + bytes_a;
             ldb = static_cast<int>(pitch_b);
+        }
+        if (stage_c) {
+            unsigned char* c_copy = scratch + bytes_a + bytes_b;
+            if (epi == kEpiLinear && beta != 0.0f) {
+                if (csz == 4) {
+                    launch_copy_rows<uint32_t, true>(ctx, c_copy, c, m, n, ldc, pitch_c, stream);
+                } else {
+                    launch_copy_rows<uint16_t, true>(ctx, c_copy, c, m, n, ldc, pitch_c, stream);
+                }
+            }
+            c = c_copy;
+            ldc = static_cast<int>(pitch_c);
         }
         CKL_TRY_CUDA(cudaGetLastError());
     }
@@ -785,7 +816,6 @@ int gemm_impl(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, 
     p.ldc = ldc;
     p.alpha = alpha;
     p.beta = beta;
-    const size_t csz = dtype_size(c_dtype);
     p.c_vec = (reinterpret_cast<uintptr_t>(c) % 16 == 0 && (static_cast<size_t>(ldc) * csz) % 16 == 0)
                   ? 1
                   : 0;
@@ -842,11 +872,22 @@ int gemm_impl(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, 
             p.sk_epoch = epoch;
         }
     }
+    int rc = CKL_OK;
     switch (c_dtype) {
-        case CKL_F32: return launch_umma_out<float>(plan.mode, ta, tb, tc, p, plan.grid, stream);
-        case CKL_F16: return launch_umma_out<__half>(plan.mode, ta, tb, tc, p, plan.grid, stream);
-        default: return launch_umma_out<__nv_bfloat16>(plan.mode, ta, tb, tc, p, plan.grid, stream);
+        case CKL_F32: rc = launch_umma_out<float>(plan.mode, ta, tb, tc, p, plan.grid, stream); break;
+        case CKL_F16: rc = launch_umma_out<__half>(plan.mode, ta, tb, tc, p, plan.grid, stream); break;
+        default: rc = launch_umma_out<__nv_bfloat16>(plan.mode, ta, tb, tc, p, plan.grid, stream); break;
     }
+    if (rc == CKL_OK && stage_c) {
+        // the aligned copy of C goes to the caller's matrix
+        if (csz == 4) {
+            launch_copy_rows<uint32_t, false>(ctx, c_user, c, m, n, ldc, static_cast<size_t>(ldc_user), stream);
+        } else {
+            launch_copy_rows<uint16_t, false>(ctx, c_user, c, m, n, ldc, static_cast<size_t>(ldc_user), stream);
+        }
+        CKL_TRY_CUDA(cudaGetLastError());
+    }
+    return rc;
 }
 
 int ensure_staging(Staging* s, size_t bytes) {

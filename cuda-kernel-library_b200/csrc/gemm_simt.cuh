@@ -163,31 +163,44 @@ __global__ void bias_relu_kernel(float* c, const float* __restrict__ bias, int m
     }
 }
 
-// Copies a rows x cols matrix of 16-bit elements from any address and pitch into a buffer whose
-// pitch (a multiple of 8 elements) and base are 16-byte aligned, so that TMA can describe it.
-// One thread moves 8 consecutive elements: eight 2-byte loads (any alignment), one 16-byte
-// store.  The padding columns of the last group are written as zero.  Pure copy, HBM-bound.
+// Copies a rows x cols matrix of 2- or 4-byte elements between a buffer of any address and
+// pitch and one whose base and pitch are 16-byte aligned (so that TMA can describe it).  One
+// thread moves one 16-byte group of the aligned side: kDstAligned packs scalar loads into one
+// 16-byte store (padding elements of the last group of a row are written as zero), otherwise
+// one 16-byte load is scattered with scalar stores (elements past `cols` are dropped).  Pure
+// copy, HBM-bound.
+template <typename T, bool kDstAligned>
 __global__ void __launch_bounds__(256)
-repack_rows_kernel(uint16_t* __restrict__ dst, const uint16_t* __restrict__ src, int rows, int cols,
-                   size_t src_pitch, size_t dst_pitch) {
-    const size_t groups_per_row = (static_cast<size_t>(cols) + 7) / 8;
+copy_rows_kernel(T* __restrict__ dst, const T* __restrict__ src, int rows, int cols, size_t src_pitch,
+                 size_t dst_pitch) {
+    constexpr int kPer = 16 / static_cast<int>(sizeof(T));
+    const size_t groups_per_row = (static_cast<size_t>(cols) + kPer - 1) / kPer;
     const size_t total = groups_per_row * static_cast<size_t>(rows);
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
     for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
         const size_t r = i / groups_per_row;
-        const int c0 = static_cast<int>(i - r * groups_per_row) * 8;
-        const uint16_t* s = src + r * src_pitch + c0;
-        uint16_t v[8];
+        const int c0 = static_cast<int>(i - r * groups_per_row) * kPer;
+        const T* s = src + r * src_pitch + c0;
+        T* d = dst + r * dst_pitch + c0;
+        union {
+            uint4 vec;
+            T elem[kPer];
+        } v;
+        if constexpr (kDstAligned) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            v[e] = (c0 + e < cols) ? s[e] : static_cast<uint16_t>(0);
+            for (int e = 0; e < kPer; ++e) {
+                v.elem[e] = (c0 + e < cols) ? s[e] : static_cast<T>(0);
+            }
+            *reinterpret_cast<uint4*>(d) = v.vec;
+        } else {
+            v.vec = *reinterpret_cast<const uint4*>(s);
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) {
+                if (c0 + e < cols) {
+                    d[e] = v.elem[e];
+                }
+            }
         }
-        uint4 out;
-        out.x = v[0] | (static_cast<uint32_t>(v[1]) << 16);
-        out.y = v[2] | (static_cast<uint32_t>(v[3]) << 16);
-        out.z = v[4] | (static_cast<uint32_t>(v[5]) << 16);
-        out.w = v[6] | (static_cast<uint32_t>(v[7]) << 16);
-        *reinterpret_cast<uint4*>(dst + r * dst_pitch + c0) = out;
     }
 }
 

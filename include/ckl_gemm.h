@@ -82,7 +82,9 @@ int ckl_gemm_bf16(const void* a, const void* b, void* c, int c_dtype, int m, int
  * m*n*k = 2^28 on it copies the offending operand(s) into a per-stream scratch
  * buffer with an aligned pitch (one copy kernel each, scratch allocated on first
  * use: make that call outside stream capture) and runs the tensor-core kernel
- * on the copies, so an odd leading dimension no longer costs the tensor cores. */
+ * on the copies, so an odd leading dimension no longer costs the tensor cores.
+ * On such problems a C that rules out 16-byte accesses (base or ldc*sizeof)
+ * is likewise computed into an aligned copy and copied out by one more pass. */
 int ckl_gemm_ex(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, int m, int n,
                 int k, int lda, int ldb, int ldc, float alpha, float beta, int algo,
                 ckl_stream_t stream);
@@ -151,7 +153,7 @@ typedef struct ckl_plan {
     int sk_units;       /* CTAs (or pairs) sharing the split tiles */
     long long sk_iters; /* total k-block iterations in the split region */
     size_t workspace_bytes;
-    int repack;         /* 1: A and/or B are first copied to a 128-byte-aligned pitch (below) */
+    int repack;         /* 1: A, B and/or C travel through copies with a 128-byte-aligned pitch */
 } ckl_plan;
 int ckl_plan_gemm(int m, int n, int k, int lda, int ldb, int ldc, int a_align, int b_align,
                   int algo, int sm_count, ckl_plan* out);

@@ -488,6 +488,33 @@ def test_unaligned_operands_are_repacked_and_match_the_oracle(env, shape):
     env.gate(dc.cpu().numpy(), ref, k, ckl.F32, f"repack, odd bases {m}x{n}x{k}")
 
 
+def test_unaligned_c_alone_is_staged_and_neighbours_are_untouched(env):
+    """A and B legal, C with an odd pitch (a view of a wider matrix): the result is written
+    through an aligned copy and copied out; the column beside the view keeps its contents."""
+    ckl, orc = env.ckl, env.orc
+    m, n, k, ldc = 1024, 1000, 1024, 1001
+    fa = orc.random_matrix(m, k, 0x1111 + m)
+    fb = orc.random_matrix(k, n, 0x2222 + n)
+    fc = orc.random_matrix(m, n, 0x9ABC + k)
+    for dt, cdt, tdt, beta in [(ckl.BF16, ckl.BF16, torch.bfloat16, 0.5), (ckl.F16, ckl.F32, torch.float32, 1.0),
+                               (ckl.F16, ckl.F16, torch.float16, 0.0)]:
+        da, ra = env.narrow_dev(fa, dt)
+        db, rb = env.narrow_dev(fb, dt)
+        wide = torch.full((m, ldc), 7.0, device="cuda", dtype=tdt)
+        if cdt == ckl.F32:
+            rc = fc
+            wide[:, :n] = torch.from_numpy(fc).cuda()
+        else:
+            dc, rc = env.narrow_dev(fc, cdt)
+            wide[:, :n] = dc
+        ckl.gemm_ex(dt, da, db, wide, cdt, m, n, k, k, n, ldc, 1.0, beta)
+        torch.cuda.synchronize()
+        assert ckl.last_plan().repack == 1
+        assert bool((wide[:, n] == 7.0).all())
+        ref, _ = orc.gemm_reference_mt(ra, rb, rc if beta != 0.0 else None, 1.0, beta)
+        env.gate(env.c_to_host(wide[:, :n].contiguous(), cdt), ref, k, cdt, f"staged C out={cdt} beta={beta}")
+
+
 def test_descriptors_are_cached_and_the_plan_is_reported(env):
     """A repeated call encodes no TMA descriptor (they are cached per device by address, shape,
     pitch, type and box), a call on other buffers encodes its own, and ckl_last_plan reports
