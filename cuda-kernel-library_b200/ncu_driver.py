@@ -57,6 +57,34 @@ def main() -> None:
         print(f"sgemm {m}x{n}x{k} fp32 beta={args.beta}: {ms:.4f} ms, "
               f"{2.0 * m * n * k / ms / 1e9:.2f} TFLOP/s (last of {args.iters} launches)")
         return
+    if args.algo == "helpers":
+        # the memory-bound helper kernels, one launch each per iteration, on matrices larger
+        # than L2: m x n FP32 / BF16 with n taken from --n (bias+ReLU pass, C = beta*C, the
+        # post-gather interleave, the column-block scatter to 4 local matrices, the copy to an
+        # aligned pitch, the bandwidth probe)
+        m, n = args.m, args.n
+        c32 = torch.randn(m, n, device="cuda")
+        bias = torch.randn(n, device="cuda")
+        c16 = torch.randn(m, n, device="cuda").to(torch.bfloat16)
+        parts = 4
+        blocks = torch.randn(parts, m, n // parts, device="cuda").to(torch.bfloat16)
+        full = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        dsts = [torch.empty(m, n, device="cuda", dtype=torch.bfloat16) for _ in range(parts)]
+        odd = torch.randn(m, n - 1, device="cuda").to(torch.bfloat16)          # pitch not 16-byte aligned
+        even = torch.randn(n - 1, n, device="cuda").to(torch.bfloat16)
+        out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        for _ in range(args.iters):
+            ckl.gemm_bias_relu(c32, bias, m, n)
+            ckl.gemm_ex(ckl.BF16, c16, c16, c16, ckl.BF16, m, n, 0, 8, n, n, 1.0, 0.5)      # k = 0: C = beta*C
+            ckl.assemble_column_blocks(full, blocks, 2, m, n // parts, parts)
+            ckl.scatter_column_block(dsts, blocks[1], 2, m, n // parts, n, n // parts)
+            ckl.gemm_ex(ckl.BF16, odd, even, out, ckl.BF16, m, n, n - 1, n - 1, n, n, 1.0, 0.0)  # copies A first
+            ckl.stream_copy(full, c16, m * n * 2)
+        torch.cuda.synchronize()
+        ckl.device_status()
+        print(f"helpers on {m} x {n}: bias_relu, scale_c, assemble_column_blocks, scatter_column_block, "
+              f"copy_rows, stream_copy launched {args.iters} times each")
+        return
     if args.algo == "trsm":
         # the blocked triangular solve: m x m lower triangle, n right-hand sides (k is ignored)
         m, n = args.m, args.n
@@ -74,7 +102,7 @@ def main() -> None:
         return
     algos = {ckl.algo_name(i): i for i in range(ckl.NUM_ALGOS)}
     if args.algo not in algos:
-        raise SystemExit(f"--algo must be one of {sorted(algos) + ['sgemm', 'trsm']}")
+        raise SystemExit(f"--algo must be one of {sorted(algos) + ['sgemm', 'trsm', 'helpers']}")
     tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
     cdt = {"f16": ckl.F16, "bf16": ckl.BF16, "f32": ckl.F32}
     m, n, k = args.m, args.n, args.k

@@ -11,7 +11,8 @@ report, a readable detail page and a record of the commit, toolkit and driver.
 
 `size` is one number (a cube) or MxNxK; `kernel` overrides the kernel-name filter (default:
 umma_gemm_kernel; sgemm_kernel, simt_gemm_kernel and trsm_diag_block_kernel for the variants
-sgemm, simt and trsm).
+sgemm, simt and trsm; the variant helpers captures one launch of each memory-bound helper
+kernel).
 
 Output: <out>/<round_name>/<variant>_<size>.ncu-rep, the matching .txt (details page) and
 round_meta.txt; <out> defaults to ./ncu_rounds (--out to change).
@@ -52,7 +53,11 @@ def tool_output(cmd: list[str]) -> str:
         return "unknown"
 
 
-DEFAULT_KERNEL = {"sgemm": "sgemm_kernel", "simt": "simt_gemm_kernel", "trsm": "trsm_diag_block_kernel"}
+DEFAULT_KERNEL = {"sgemm": "sgemm_kernel", "simt": "simt_gemm_kernel", "trsm": "trsm_diag_block_kernel",
+                  "helpers": "bias_relu_kernel|scale_c_kernel|assemble_column_blocks_kernel|"
+                             "scatter_column_block_kernel|copy_rows_kernel|stream_copy_kernel"}
+# launches captured per configuration (after two skipped): the helpers variant wants one of each
+LAUNCH_COUNT = {"helpers": 6}
 
 
 def parse_pair(pair: str) -> tuple[str, tuple[int, int, int], str]:
@@ -118,7 +123,9 @@ def main() -> int:
             ncu += ["--section", section]
         # skip the two warm launches of the driver; trsm launches several diagonal-block kernels
         # per solve, any settled one serves
-        ncu += ["--kernel-name", f"regex:{kernel}", "--launch-skip", "2", "--launch-count", "1",
+        skip = "6" if variant == "helpers" else "2"      # one whole warm round of the six helpers
+        ncu += ["--kernel-name", f"regex:{kernel}", "--launch-skip", skip, "--launch-count",
+                str(LAUNCH_COUNT.get(variant, 1)),
                 "--force-overwrite", "--export", base, *cmd]
         run = subprocess.run(ncu, capture_output=True, text=True)
         if run.returncode != 0:

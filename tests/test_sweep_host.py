@@ -106,6 +106,7 @@ def test_ncu_round_commands(tmp_path, monkeypatch):
     assert "regex:streamk_fixup_kernel" in profiled[3]
     assert "umma_2cta_streamk_1024x1024x32768_streamk_fixup_kernel" in profiled[3]
     assert mod.parse_pair("simt:129x257x193")[2] == "simt_gemm_kernel"
+    assert "scatter_column_block_kernel" in mod.parse_pair("helpers:8192")[2]
     assert not any("umma_1cta" in c for c in calls)
     assert (tmp_path / "r1" / "umma_2cta_wide_8192.txt").read_text().strip() == "details page"
     meta = (tmp_path / "r1" / "round_meta.txt").read_text()
