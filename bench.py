@@ -465,67 +465,11 @@ def run_ours(args) -> None:
     # ---- gathered variant (N > 1): every rank ends with the whole row-major C ----------------
     gathered = None
     if world > 1 and sharded.even_shards(N, world):
-        gathered = {}
-        full_ptr = comm.alloc_shared(M * N * 2)
-        def gstep():
-            op.gathered(comm, a, b, c, full_ptr, ALPHA, BETA, stream=stream)
-        for _ in range(3):
-            gstep()
-        barrier()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record(stream)
-        for _ in range(args.steps):
-            gstep()
-        g1.record(stream)
-        barrier()
-        gms = all_max(g0.elapsed_time(g1)) / args.steps
-        # parity, outside the timed region: one step from the seeded C_in; every rank checks the
-        # WHOLE assembled C against the unsharded kernel run here on the full B and C_in
-        c.copy_(c_in)
-        gstep()
-        got_full = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
-        ckl.stream_copy(got_full, full_ptr, M * N * 2, stream)
-        ref_full = c_full.cuda()
-        b_dev_full = b_full.cuda()
-        ckl.gemm_ex(ckl.BF16, a, b_dev_full, ref_full, ckl.BF16, M, N, K, K, N, N, ALPHA, BETA, 0, stream)
-        torch.cuda.synchronize()
-        cmp = compare(torch, got_full, ref_full)
-        own_ok = torch.equal(got_full[:, col0:col0 + w], c)
-        tol = 2e-2 * math.sqrt(K / 4096.0) * cmp["max_abs_value"]
-        ok = own_ok and cmp["rel_frobenius"] <= 1e-3 and cmp["max_abs_diff"] <= tol
-        parity = {"ok_on_every_rank": all_max(0.0 if ok else 1.0) == 0.0,
-                  "max_abs_diff": all_max(cmp["max_abs_diff"]),
-                  "rel_frobenius": all_max(cmp["rel_frobenius"]),
-                  "bit_equal_on_every_rank": all_max(0.0 if cmp["bit_equal"] else 1.0) == 0.0,
-                  "checked": "whole C on every rank against the unsharded kernel on the same inputs "
-                             "(rel. Frobenius <= 1e-3, max error <= 2e-2*sqrt(K/4096)*max|C|); the "
-                             "rank's own block bit for bit against its local c_shard"}
-        del got_full, ref_full, b_dev_full
-        gathered = {"value": 2.0 * M * N * K / (gms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                    "ms_per_step": gms, "parity": parity,
-                    "note": "ckl_gemm_gathered: GEMM in row panels, each panel's column block "
-                            "written into every rank's C by this library's copy kernel (plain "
-                            "peer stores over NVLink) while the next panel multiplies"}
-        comm.free_shared(full_ptr)
-        # the same through NCCL: GEMM, all_gather_into_tensor, interleave kernel, one after another
-        staging = torch.empty(world, M, w, dtype=torch.bfloat16, device="cuda")
-        full = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
-        def nstep():
-            step()
-            op.gather(c, staging, full, stream=stream)
-        for _ in range(3):
-            nstep()
-        barrier()
-        g0.record(stream)
-        for _ in range(args.steps):
-            nstep()
-        g1.record(stream)
-        barrier()
-        nms = all_max(g0.elapsed_time(g1)) / args.steps
-        gathered["nccl_all_gather_variant"] = {
-            "value": 2.0 * M * N * K / (nms * 1e-3) / 1e12, "ms_per_step": nms,
-            "note": "GEMM + NCCL all-gather of the C column blocks + interleave kernel"}
-        del staging, full
+        try:
+            gathered = run_gathered(torch, ckl, op, comm, world, a, b, c, c_in, b_full, c_full, col0, w,
+                                    step, barrier, all_max, stream, args.steps)
+        except Exception as exc:      # keep the headline line; say what went wrong
+            gathered = {"error": f"{type(exc).__name__}: {exc}"}
 
     # ---- end to end through the host-buffer entry point --------------------------------------
     e2e_steps = max(3, min(args.steps, 10))
@@ -569,7 +513,10 @@ def run_ours(args) -> None:
     # ---- BASELINE config 5 (MLP-shaped, weights N-sharded) on N > 1 GPUs ----------------------
     mlp = None
     if world > 1:
-        mlp = run_mlp_sharded(torch, dist, ckl, sharded, comm, world, rank, all_max, barrier)
+        try:
+            mlp = run_mlp_sharded(torch, dist, ckl, sharded, comm, world, rank, all_max, barrier)
+        except Exception as exc:
+            mlp = {"error": f"{type(exc).__name__}: {exc}"}
 
     # ---- comparator on the same box: cuBLAS through torch.matmul (not the product) ------------
     cublas_tflops = cublas_beta_tflops = cublas_sustained = None
@@ -590,7 +537,10 @@ def run_ours(args) -> None:
         del c_ref, ref_b
         if world == 1:
             time.sleep(1.0)
-            configs = other_configs(torch, ckl, float(peaks["bf16_tflops"]))
+            try:
+                configs = other_configs(torch, ckl, float(peaks["bf16_tflops"]))
+            except Exception as exc:
+                configs = [{"error": f"{type(exc).__name__}: {exc}"}]
 
     if rank == 0:
         tflops = 2.0 * M * N * K / (ms_per_step * 1e-3) / 1e12
@@ -648,6 +598,72 @@ def run_ours(args) -> None:
         comm.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_gathered(torch, ckl, op, comm, world, a, b, c, c_in, b_full, c_full, col0, w, step, barrier,
+                 all_max, stream, steps) -> dict:
+    """The step that leaves the whole row-major C on every rank: ckl_gemm_gathered timed over
+    `steps` steps, its parity on every rank, and the NCCL all-gather form beside it."""
+    full_ptr = comm.alloc_shared(M * N * 2)
+    def gstep():
+        op.gathered(comm, a, b, c, full_ptr, ALPHA, BETA, stream=stream)
+    for _ in range(3):
+        gstep()
+    barrier()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record(stream)
+    for _ in range(steps):
+        gstep()
+    g1.record(stream)
+    barrier()
+    gms = all_max(g0.elapsed_time(g1)) / steps
+    # parity, outside the timed region: one step from the seeded C_in; every rank checks the
+    # WHOLE assembled C against the unsharded kernel run here on the full B and C_in
+    c.copy_(c_in)
+    gstep()
+    got_full = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ckl.stream_copy(got_full, full_ptr, M * N * 2, stream)
+    ref_full = c_full.cuda()
+    b_dev_full = b_full.cuda()
+    ckl.gemm_ex(ckl.BF16, a, b_dev_full, ref_full, ckl.BF16, M, N, K, K, N, N, ALPHA, BETA, 0, stream)
+    torch.cuda.synchronize()
+    cmp = compare(torch, got_full, ref_full)
+    own_ok = torch.equal(got_full[:, col0:col0 + w], c)
+    tol = 2e-2 * math.sqrt(K / 4096.0) * cmp["max_abs_value"]
+    ok = own_ok and cmp["rel_frobenius"] <= 1e-3 and cmp["max_abs_diff"] <= tol
+    parity = {"ok_on_every_rank": all_max(0.0 if ok else 1.0) == 0.0,
+              "max_abs_diff": all_max(cmp["max_abs_diff"]),
+              "rel_frobenius": all_max(cmp["rel_frobenius"]),
+              "bit_equal_on_every_rank": all_max(0.0 if cmp["bit_equal"] else 1.0) == 0.0,
+              "checked": "whole C on every rank against the unsharded kernel on the same inputs "
+                         "(rel. Frobenius <= 1e-3, max error <= 2e-2*sqrt(K/4096)*max|C|); the "
+                         "rank's own block bit for bit against its local c_shard"}
+    del got_full, ref_full, b_dev_full
+    gathered = {"value": 2.0 * M * N * K / (gms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "ms_per_step": gms, "parity": parity,
+                "note": "ckl_gemm_gathered: GEMM in row panels, each panel's column block "
+                        "written into every rank's C by this library's copy kernel (plain "
+                        "peer stores over NVLink) while the next panel multiplies"}
+    comm.free_shared(full_ptr)
+    # the same through NCCL: GEMM, all_gather_into_tensor, interleave kernel, one after another
+    staging = torch.empty(world, M, w, dtype=torch.bfloat16, device="cuda")
+    full = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    def nstep():
+        step()
+        op.gather(c, staging, full, stream=stream)
+    for _ in range(3):
+        nstep()
+    barrier()
+    g0.record(stream)
+    for _ in range(steps):
+        nstep()
+    g1.record(stream)
+    barrier()
+    nms = all_max(g0.elapsed_time(g1)) / steps
+    gathered["nccl_all_gather_variant"] = {
+        "value": 2.0 * M * N * K / (nms * 1e-3) / 1e12, "ms_per_step": nms,
+        "note": "GEMM + NCCL all-gather of the C column blocks + interleave kernel"}
+    return gathered
 
 
 def run_mlp_sharded(torch, dist, ckl, sharded, comm, world, rank, all_max, barrier) -> dict:
