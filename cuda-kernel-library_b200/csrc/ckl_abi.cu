@@ -331,8 +331,29 @@ Schedule make_schedule(int m, int n, int k, int mode, int max_units, int want_sk
             if (rem * 10 > max_units * 6) {
                 return s;
             }
-        } else if (tiles * 4 > max_units * 3 || sk_iters / max_units < 8) {
-            return s;
+            // Folding a wave into a thin remainder must leave every unit a whole tile to hide
+            // the reduction behind; with a single full wave it would split EVERY tile and end
+            // in the separate fix-up pass (2048 x 2816 x 2048: 625 TFLOP/s against 864 unsplit).
+            if (tiles - sk_tiles < max_units) {
+                return s;
+            }
+            // Parking and adding a partial tile costs the same whatever k is; below k = 4096
+            // it is not won back (4096 x 4096 x 2048: 1281 split against 1425 unsplit,
+            // 4096 x 2816 x 1024: 809 against 1010; from k = 4096 on the split is level or ahead).
+            if (static_cast<long long>(s.k_blocks) * d.tile_k < 4096) {
+                return s;
+            }
+        } else {
+            // Every tile would be cut over f units and finished by the fix-up pass, which costs
+            // about as much as 40 k blocks of 64 (20 of 128) of one tile; the cut saves
+            // k_blocks * (1 - 1/f) of them (1536^3, f = 2, 24 k blocks: 369 TFLOP/s split
+            // against 530 unsplit; 1024 x 1024 x 8192, f = 4, 128 k blocks: 676 against 409).
+            const long long f = max_units / tiles;
+            const long long saved = f >= 2 ? static_cast<long long>(s.k_blocks) * (f - 1) / f : 0;
+            const long long pass_cost = d.tile_k >= 128 ? 20 : 40;
+            if (tiles * 4 > max_units * 3 || saved < pass_cost) {
+                return s;
+            }
         }
     }
     if (sk_iters < max_units) {
@@ -942,8 +963,16 @@ int ckl_bias_relu_f32(float* c, const float* bias, int m, int n, int ldc, ckl_st
         return fail(CKL_ERR_INVALID_ARG, "ckl_bias_relu_f32: null pointer or ldc < n");
     }
     const long long total = static_cast<long long>(m) * n;
-    const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148LL * 16));
-    bias_relu_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(c, bias, m, n, ldc);
+    const bool vec = n % 4 == 0 && ldc % 4 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0 &&
+                     reinterpret_cast<uintptr_t>(bias) % 16 == 0;
+    if (vec) {
+        const int blocks = static_cast<int>(std::min<long long>((total / 4 + 255) / 256, 148LL * 16));
+        bias_relu_vec4_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            reinterpret_cast<float4*>(c), reinterpret_cast<const float4*>(bias), m, n / 4, ldc / 4);
+    } else {
+        const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148LL * 16));
+        bias_relu_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(c, bias, m, n, ldc);
+    }
     CKL_TRY_CUDA(cudaGetLastError());
     return CKL_OK;
 }

@@ -163,6 +163,26 @@ __global__ void bias_relu_kernel(float* c, const float* __restrict__ bias, int m
     }
 }
 
+// The same pass four columns at a time, for n and ldc multiples of 4 and 16-byte aligned
+// pointers: one 16-byte load and store per thread instead of four 4-byte ones.
+__global__ void __launch_bounds__(256)
+bias_relu_vec4_kernel(float4* c, const float4* __restrict__ bias, int m, int n4, int ldc4) {
+    const long long total = static_cast<long long>(m) * n4;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long r = i / n4;
+        const int col = static_cast<int>(i - r * n4);
+        float4* dst = c + r * ldc4 + col;
+        float4 v = *dst;
+        const float4 bv = __ldg(bias + col);
+        v.x = fmaxf(v.x + bv.x, 0.0f);
+        v.y = fmaxf(v.y + bv.y, 0.0f);
+        v.z = fmaxf(v.z + bv.z, 0.0f);
+        v.w = fmaxf(v.w + bv.w, 0.0f);
+        *dst = v;
+    }
+}
+
 // Copies a rows x cols matrix of 2- or 4-byte elements between a buffer of any address and
 // pitch and one whose base and pitch are 16-byte aligned (so that TMA can describe it).  One
 // thread moves one 16-byte group of the aligned side: kDstAligned packs scalar loads into one

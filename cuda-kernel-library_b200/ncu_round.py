@@ -54,7 +54,7 @@ def tool_output(cmd: list[str]) -> str:
 
 
 DEFAULT_KERNEL = {"sgemm": "sgemm_kernel", "simt": "simt_gemm_kernel", "trsm": "trsm_diag_block_kernel",
-                  "helpers": "bias_relu_kernel|scale_c_kernel|assemble_column_blocks_kernel|"
+                  "helpers": "bias_relu|scale_c_kernel|assemble_column_blocks_kernel|"
                              "scatter_column_block_kernel|copy_rows_kernel|stream_copy_kernel"}
 # launches captured per configuration (after two skipped): the helpers variant wants one of each
 LAUNCH_COUNT = {"helpers": 6}

@@ -134,9 +134,18 @@ def test_dispatch_follows_the_reference_contract(ckl):
     # with a short k per unit the single-CTA tiles keep the job (32 tiles x 4 CTAs)
     p = ckl.plan_gemm(1024, 1024, 8192)
     assert p.algo == ckl.ALGO_UMMA_SK and p.units == 128
-    # a thin last wave is split too, behind whole tiles (34 tiles left for 74 pairs)
+    # a thin last wave is split too, behind whole tiles (14 tiles left for 74 pairs), but only
+    # from k = 4096 on: below that the parked partials cost more than the idle SMs
+    p = ckl.plan_gemm(2048, 2816, 4096)
+    assert p.algo == ckl.ALGO_UMMA_2CTA_SK and (p.dp_tiles, p.sk_tiles, p.units) == (74, 14, 74)
     p = ckl.plan_gemm(4096, 4096, 2048)
-    assert p.algo == ckl.ALGO_UMMA_2CTA_SK and (p.dp_tiles, p.sk_tiles, p.units) == (222, 34, 74)
+    assert p.algo == ckl.ALGO_UMMA_2CTA and p.sk_tiles == 0
+    # a remainder too thin to occupy the units is not folded into the only full wave
+    assert ckl.plan_gemm(2048, 2816, 2048).sk_tiles == 0
+    # fewer tiles than units: cut every tile only when the cut saves more than the fix-up pass costs
+    assert ckl.plan_gemm(1536, 1536, 1536).sk_tiles == 0
+    p = ckl.plan_gemm(256, 8192, 8192)
+    assert p.sk_tiles == 32 and p.units == 64
     # from k = 4096 on the 256x512 tile takes over where its waves fill as well
     assert ckl.plan_gemm(4096, 4096, 4096).algo == ckl.ALGO_UMMA_2CTA_WIDE
     # a nearly full last wave is not
