@@ -315,9 +315,12 @@ Schedule make_schedule(int m, int n, int k, int mode, int max_units, int want_sk
         return s;
     }
     int sk_tiles = rem;
-    // Give every unit a few k blocks of split work: if the remainder alone is
-    // too thin, fold one full wave into the split region as well.
-    if (full_waves >= 1 && static_cast<long long>(rem) * s.k_blocks < 4LL * max_units) {
+    // Give every unit a run of k blocks of split work worth its parked partial tile (2048 k):
+    // if the remainder alone is too thin, fold one full wave into the split region as well.
+    // (2048 x 2816 x 4096: 14 tiles over 74 pairs leave each pair 6 k blocks of 128 and one
+    // parked partial tile, and the split measures no faster than none: 1041 against 1077.)
+    const long long thin = d.tile_k >= 128 ? 16 : 32;
+    if (full_waves >= 1 && static_cast<long long>(rem) * s.k_blocks < thin * max_units) {
         sk_tiles = rem + max_units;
     }
     const long long sk_iters = static_cast<long long>(sk_tiles) * s.k_blocks;
@@ -408,9 +411,27 @@ int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_al
             return static_cast<double>(tiles) / static_cast<double>(waves * max_pairs);
         };
         const int wide_min_k = c_traffic >= 8 ? 8192 : 4096;  // FP32 C read and written: longer drain
-        const bool use_wide = max_pairs > 0 && wide_tiles * 5 >= max_pairs * 4LL && k >= wide_min_k &&
-                              (n % 512 == 0 || n % 512 > 384) &&
-                              wave_fill(wide_tiles) >= wave_fill(pair_tiles) - 0.02;
+        bool use_wide = max_pairs > 0 && wide_tiles * 5 >= max_pairs * 4LL && k >= wide_min_k &&
+                        (n % 512 == 0 || n % 512 > 384) &&
+                        wave_fill(wide_tiles) >= wave_fill(pair_tiles) - 0.02;
+        // Between k = 4096 and 8192 the exposed epilogue is 5-9 % of a tile, and the 256x256
+        // tile with its split last wave has no quantisation loss at all: there the wide tile
+        // keeps the job only for at most two waves or when its own last wave is nearly full
+        // (5120^3, last wave 70 % full: 1171-1281 TFLOP/s wide against 1345-1385 split
+        // 256x256; 2048 x 12288 x 4096: 1137-1178 against 1239-1278; 4096^3, two waves:
+        // 1455-1472 against 1415-1447).
+        if (use_wide && k < 8192 && wide_tiles > 2LL * max_pairs && wave_fill(wide_tiles) < 0.95) {
+            use_wide = false;
+        }
+        // Row pitches that are not multiples of 128 bytes double the L2 requests of every TMA
+        // box row; the wide tile needs a quarter fewer of them per MMA cycle and then wins from
+        // shorter k already, provided its waves fill (3000^3: 986 against 844 TFLOP/s).
+        const bool odd_pitch = (static_cast<long long>(lda) * 2) % 128 != 0 ||
+                               (static_cast<long long>(ldb) * 2) % 128 != 0;
+        if (!use_wide && odd_pitch && max_pairs > 0 && k >= 2048 && c_traffic < 8 &&
+            wide_tiles * 5 >= max_pairs * 4LL && wave_fill(wide_tiles) >= 0.9) {
+            use_wide = true;
+        }
         // Fewer 256x256 tiles than half the pairs: split every tile over a whole number of
         // pairs, provided each still gets a long run of k blocks (128 k each); measured better
         // than 128x256 single-CTA tiles split the same way (half the B traffic per SM).

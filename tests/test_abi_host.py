@@ -134,10 +134,21 @@ def test_dispatch_follows_the_reference_contract(ckl):
     # with a short k per unit the single-CTA tiles keep the job (32 tiles x 4 CTAs)
     p = ckl.plan_gemm(1024, 1024, 8192)
     assert p.algo == ckl.ALGO_UMMA_SK and p.units == 128
-    # a thin last wave is split too, behind whole tiles (14 tiles left for 74 pairs), but only
-    # from k = 4096 on: below that the parked partials cost more than the idle SMs
-    p = ckl.plan_gemm(2048, 2816, 4096)
-    assert p.algo == ckl.ALGO_UMMA_2CTA_SK and (p.dp_tiles, p.sk_tiles, p.units) == (74, 14, 74)
+    # a last wave that is at most 60 % full is split too, behind whole tiles (44 tiles left for
+    # 74 pairs), but only from k = 4096 on: below that the parked partials cost more than the
+    # idle SMs; a remainder too thin to give every pair 2048 k of split work takes a whole
+    # wave with it when two or more exist (4 + 74 tiles), and is left alone otherwise
+    p = ckl.plan_gemm(4000, 3000, 5000)
+    assert p.algo == ckl.ALGO_UMMA_2CTA_SK and (p.dp_tiles, p.sk_tiles, p.units) == (148, 44, 74)
+    p = ckl.plan_gemm(16384, 1792, 4096)
+    assert p.algo == ckl.ALGO_UMMA_2CTA_SK and (p.dp_tiles, p.sk_tiles, p.units) == (370, 78, 74)
+    assert ckl.plan_gemm(2048, 2816, 4096).sk_tiles == 0
+    # between k = 4096 and 8192 the wide tile needs nearly full waves (or at most two)
+    assert ckl.plan_gemm(5120, 5120, 5120).algo == ckl.ALGO_UMMA_2CTA_SK
+    assert ckl.plan_gemm(6144, 6144, 6144).algo == ckl.ALGO_UMMA_2CTA_WIDE
+    # unaligned row pitches: the wide tile from shorter k on, when its waves fill
+    assert ckl.plan_gemm(3000, 3000, 3000).algo == ckl.ALGO_UMMA_2CTA_WIDE
+    assert ckl.plan_gemm(3072, 3072, 3072).algo == ckl.ALGO_UMMA_2CTA
     p = ckl.plan_gemm(4096, 4096, 2048)
     assert p.algo == ckl.ALGO_UMMA_2CTA and p.sk_tiles == 0
     # a remainder too thin to occupy the units is not folded into the only full wave
