@@ -319,7 +319,8 @@ Schedule make_schedule(int m, int n, int k, int mode, int max_units, int want_sk
     // if the remainder alone is too thin, fold one full wave into the split region as well.
     // (2048 x 2816 x 4096: 14 tiles over 74 pairs leave each pair 6 k blocks of 128 and one
     // parked partial tile, and the split measures no faster than none: 1041 against 1077.)
-    const long long thin = d.tile_k >= 128 ? 16 : 32;
+    // A forced split (tests, benchmarks) keeps the lower bar of a few k blocks per unit.
+    const long long thin = want_sk != 2 ? 4 : (d.tile_k >= 128 ? 16 : 32);
     if (full_waves >= 1 && static_cast<long long>(rem) * s.k_blocks < thin * max_units) {
         sk_tiles = rem + max_units;
     }
