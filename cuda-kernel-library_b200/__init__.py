@@ -26,8 +26,8 @@ OK, ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE, ERR_TOO_LARGE = rang
 F32, F16, BF16 = 0, 1, 2
 # ckl_algo
 (ALGO_AUTO, ALGO_SIMT, ALGO_UMMA_1CTA, ALGO_UMMA_SK, ALGO_UMMA_2CTA, ALGO_UMMA_2CTA_SK,
- ALGO_UMMA_2CTA_WIDE, ALGO_UMMA_2CTA_WIDE_SK) = range(8)
-NUM_ALGOS = 8
+ ALGO_UMMA_2CTA_WIDE, ALGO_UMMA_2CTA_WIDE_SK, ALGO_UMMA_1CTA_N128, ALGO_UMMA_1CTA_N128_SK) = range(10)
+NUM_ALGOS = 10
 
 
 class CklError(RuntimeError):

@@ -209,7 +209,7 @@ int get_ctx(DeviceCtx** out) {
 
 size_t dtype_size(int dtype) { return dtype == CKL_F32 ? 4 : 2; }
 
-constexpr int kLastAlgo = CKL_ALGO_UMMA_2CTA_WIDE_SK;
+constexpr int kLastAlgo = CKL_ALGO_UMMA_1CTA_N128_SK;
 bool is_tensor_algo(int algo) { return algo >= CKL_ALGO_UMMA_1CTA && algo <= kLastAlgo; }
 int mode_of_algo(int algo) {
     switch (algo) {
@@ -222,7 +222,10 @@ int mode_of_algo(int algo) {
 }
 bool is_sk_algo(int algo) {
     return algo == CKL_ALGO_UMMA_SK || algo == CKL_ALGO_UMMA_2CTA_SK ||
-           algo == CKL_ALGO_UMMA_2CTA_WIDE_SK;
+           algo == CKL_ALGO_UMMA_2CTA_WIDE_SK || algo == CKL_ALGO_UMMA_1CTA_N128_SK;
+}
+bool is_narrow_algo(int algo) {
+    return algo == CKL_ALGO_UMMA_1CTA_N128 || algo == CKL_ALGO_UMMA_1CTA_N128_SK;
 }
 struct ModeDims {
     int tile_m, tile_n, tile_k;
@@ -285,9 +288,12 @@ bool tma_legal(int k, int lda, int ldb, size_t a_align, size_t b_align) {
 }
 
 // want_sk: 0 = never, 1 = always when a remainder exists, 2 = heuristic.
-Schedule make_schedule(int m, int n, int k, int mode, int max_units, int want_sk) {
+Schedule make_schedule(int m, int n, int k, int mode, int max_units, int want_sk, bool narrow = false) {
     Schedule s = {};
-    const ModeDims d = dims_of_mode(mode);
+    ModeDims d = dims_of_mode(mode);
+    if (narrow) {
+        d.tile_n = 128;  // the single-CTA kernel's 128-column form
+    }
     s.tiles_m = (m + d.tile_m - 1) / d.tile_m;
     s.tiles_n = (n + d.tile_n - 1) / d.tile_n;
     s.k_blocks = (k + d.tile_k - 1) / d.tile_k;
@@ -482,12 +488,21 @@ int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_al
         return fail(CKL_ERR_UNSUPPORTED, "no schedulable units (sm_count=%d)", sm_count);
     }
     const ModeDims d = dims_of_mode(mode);
+    bool narrow = is_narrow_algo(resolved);
     plan->mode = mode;
     plan->pair = pair;
     plan->tile_m = d.tile_m;
-    plan->tile_n = d.tile_n;
     plan->tile_k = d.tile_k;
-    plan->sched = make_schedule(m, n, k, mode, max_units, want_sk);
+    if (algo == CKL_ALGO_AUTO && mode == kModeSingle && n > 128 &&
+        2LL * ((m + d.tile_m - 1) / d.tile_m) * ((n + d.tile_n - 1) / d.tile_n) <= max_units) {
+        // 128x256 tiles would keep at most half of the SMs busy: 128x128 tiles give twice as
+        // many, each with half the main loop and half the epilogue (1536^3: 684 against 551
+        // TFLOP/s, 1024^3: 270 against 211), and where every tile is cut over several CTAs the
+        // partial tiles are half as large (1024 x 1024 x 8192: 637 against 576).
+        narrow = true;
+    }
+    plan->sched = make_schedule(m, n, k, mode, max_units, want_sk, narrow);
+    plan->tile_n = narrow ? 128 : d.tile_n;
     plan->grid = plan->sched.units * (pair ? 2 : 1);
     if (plan->sched.sk_tiles > 0) {
         plan->workspace_bytes = 2ull * static_cast<size_t>(plan->sched.units) * d.slot_bytes;
@@ -496,8 +511,12 @@ int make_plan(int m, int n, int k, int lda, int ldb, size_t a_align, size_t b_al
         if (algo == CKL_ALGO_AUTO) {
             plan->algo = mode == kModePairWide ? CKL_ALGO_UMMA_2CTA_WIDE
                          : mode == kModePair   ? CKL_ALGO_UMMA_2CTA
+                         : narrow              ? CKL_ALGO_UMMA_1CTA_N128
                                                : CKL_ALGO_UMMA_1CTA;
         }
+    }
+    if (algo == CKL_ALGO_AUTO && narrow && plan->sched.sk_tiles > 0) {
+        plan->algo = CKL_ALGO_UMMA_1CTA_N128_SK;
     }
     return CKL_OK;
 }
@@ -876,8 +895,9 @@ int gemm_impl(int ab_dtype, const void* a, const void* b, void* c, int c_dtype, 
             return rc;
         }
     }
+    p.tile_n = plan.tile_n == 128 ? 128 : 0;
     p.idesc = ptx::make_idesc_f16(ab_dtype == CKL_F16 ? 0u : 1u, 0u, 1u, plan.pair ? 256u : 128u,
-                                  256u);
+                                  plan.tile_n == 128 ? 128u : 256u);
     p.sched = plan.sched;
     p.wait_limit_ns = kWaitLimitNs;
     const WaitFault fault = g_wait_fault;
@@ -1425,6 +1445,8 @@ const char* ckl_algo_name(int algo) {
         case CKL_ALGO_UMMA_2CTA_SK: return "umma_2cta_streamk";
         case CKL_ALGO_UMMA_2CTA_WIDE: return "umma_2cta_wide";
         case CKL_ALGO_UMMA_2CTA_WIDE_SK: return "umma_2cta_wide_streamk";
+        case CKL_ALGO_UMMA_1CTA_N128: return "umma_1cta_n128";
+        case CKL_ALGO_UMMA_1CTA_N128_SK: return "umma_1cta_n128_streamk";
         default: return "unknown";
     }
 }

@@ -67,6 +67,10 @@ struct GemmParams {
     int epi_mode;
     uint32_t idesc;
     Schedule sched;
+    // Columns of an output tile.  0 means the kernel shape's own width (256, or 512 for the
+    // wide pair tile); the single-CTA kernel also runs 128-column tiles (two of its four B
+    // boxes per stage, UMMA 128x128x16), which doubles the tile count of small problems.
+    int tile_n;
     // Limit of every bounded wait in nanoseconds; 0 means kWaitLimitNs.
     unsigned long long wait_limit_ns;
     // Test hooks, both 0 in every ordinary launch.  sk_flag_skew is added to the flag value the
@@ -506,6 +510,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ptx::launch_dependents();
 
     const Schedule& sched = p.sched;
+    // Tile width: only the single-CTA shape has a narrow form.
+    const int tile_n = (kMode == kModeSingle && p.tile_n == 128) ? 128 : Cfg::kTileN;
 
     // ---- roles ----------------------------------------------------------------
     if (warp == 0) {
@@ -522,7 +528,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 int tm, tn;
                 tile_coords(sched, seg.tile, &tm, &tn);
                 const int a_row = tm * Cfg::kTileM + (kPair ? static_cast<int>(rank) * 128 : 0);
-                const int b_col = tn * Cfg::kTileN + (kPair ? static_cast<int>(rank) * 128 : 0);
+                const int b_col = tn * tile_n + (kPair ? static_cast<int>(rank) * 128 : 0);
+                const int b_boxes = kMode == kModeSingle ? tile_n / 64 : Cfg::kBBoxes;
                 for (int kb = seg.kb_begin; kb < seg.kb_end; ++kb) {
                     {
                         const bool got = detail::wait_barrier(empty_bar(stage), phase ^ 1u, ctl,
@@ -537,7 +544,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     {
                         uint32_t bar = full_bar(stage);
                         // (test hook: unit 0 may overstate its first stage, see GemmParams)
-                        const uint32_t tx = Cfg::kTxBytes +
+                        const uint32_t tx = Cfg::kTxBytes -
+                                            static_cast<uint32_t>(Cfg::kBBoxes - b_boxes) * Cfg::kKSub * Cfg::kBoxBytes +
                                             ((p.overstate_first_stage != 0 && it == 0 && unit == 0) ? 16u : 0u);
                         if constexpr (kPair) {
                             if (leader) {
@@ -559,6 +567,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             }
 #pragma unroll
                             for (int j = 0; j < Cfg::kBBoxes; ++j) {
+                                if (j >= b_boxes) {
+                                    break;  // narrow tile: columns 128-255 of the stage stay unused
+                                }
                                 // wide tile: boxes 0,1 belong to columns 0-255 of the tile,
                                 // boxes 2,3 to columns 256-511 (this CTA's 128 of each)
                                 const int box_col =
@@ -786,7 +797,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                     static_cast<int>(quad) * 32 + static_cast<int>(lane);
             const int row = tm * Cfg::kTileM + row_in_tile;
             const int row0 = row - static_cast<int>(lane);  // first row of this warp
-            const int col_base = tn * Cfg::kTileN + static_cast<int>(half) * 256;
+            const int col_base = tn * tile_n + static_cast<int>(half) * 256;
             const uint32_t t_row = tmem_base + ((quad * 32u) << 16) + acc_cols;
             // A split tile is finished either by the separate fix-up pass (every unit parks its
             // partial) or, fused, by the unit that holds the tile's first k blocks: that unit
@@ -847,7 +858,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             };
 
             // Chunks of kChunkCols columns this warp writes through the TMA path.
-            const int cols_left = p.n - col_base;
+            const int cols_left = min(p.n - col_base, tile_n);  // columns of this tile this warp drains
             const int n_chunks =
                 !tma_path || !warp_has_rows || cols_left <= 0
                     ? 0
@@ -915,8 +926,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 // so every store (and every load of the fix-up pass, which uses the same
                 // lane = row mapping) moves 512 contiguous bytes per warp.
                 float* dst = p.workspace + static_cast<size_t>(seg.slot) * Cfg::kSlotFloats + slot_part;
+                const int park_chunks = min(256, tile_n) / 32;  // a narrow tile has 4 chunks, not 8
 #pragma unroll 1
-                for (int c = 0; c < 256 / 32; ++c) {
+                for (int c = 0; c < park_chunks; ++c) {
                     uint32_t r[32];
                     ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), r);
                     ptx::tmem_ld_wait();
@@ -1068,7 +1080,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 const bool row_ok = row < p.m;
 #pragma unroll 1
                 for (int c = 0; c < 256 / 32; ++c) {
-                    if (col_base + c * 32 >= p.n) {
+                    if (col_base + c * 32 >= p.n || c * 32 >= tile_n) {
                         break;  // uniform across the warp
                     }
                     uint32_t r[32];
@@ -1156,8 +1168,9 @@ streamk_fixup_kernel(const GemmParams p) {
     const int lane = static_cast<int>(threadIdx.x) & 31;
     const int chunk = static_cast<int>(threadIdx.x) >> 5;  // 8 warps = 8 chunks of 32 columns
     const int row = tm * kTileM + (gh / kNHalves) * 32 + lane;
-    const int col0 = tn * kTileN + (gh % kNHalves) * 256 + chunk * 32;
-    if (col0 >= p.n) {
+    const int tile_n = (kTileM == 128 && kTileN == 256 && p.tile_n == 128) ? 128 : kTileN;  // narrow single-CTA tile
+    const int col0 = tn * tile_n + (gh % kNHalves) * 256 + chunk * 32;
+    if (col0 >= p.n || chunk * 32 >= tile_n) {
         return;  // uniform per warp
     }
     const float* base = p.workspace + static_cast<size_t>(gh) * 8192u + chunk * 1024 + lane * 4;

@@ -6,7 +6,8 @@
 // and the same keys in the row, plus tflops, percent of the datasheet dense
 // 16-bit peak, the C dtype and the GPU count, which the sweep's resume key uses.
 //   variant: auto | simt | umma_1cta | umma_1cta_streamk | umma_2cta |
-//            umma_2cta_streamk | umma_2cta_wide | umma_2cta_wide_streamk
+//            umma_2cta_streamk | umma_2cta_wide | umma_2cta_wide_streamk |
+//            umma_1cta_n128 | umma_1cta_n128_streamk
 //   dtype  : fp16 | bf16 (FP32 C, as the reference measures) or fp16_c16 | bf16_c16;
 //            fp32 with variant sgemm = the CUDA-core kernel behind the reference's FP32 rungs
 //     bench_all trsm blocked fp32 <m> <n> 0 [commit]   (the reference's trsm family, line 132-170)
@@ -30,7 +31,7 @@
 namespace {
 
 int algo_from_name(const std::string& name) {
-    for (int a = 0; a <= CKL_ALGO_UMMA_2CTA_WIDE_SK; ++a) {
+    for (int a = 0; a <= CKL_ALGO_UMMA_1CTA_N128_SK; ++a) {
         if (name == ckl_algo_name(a)) {
             return a;
         }

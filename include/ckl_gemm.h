@@ -53,7 +53,10 @@ typedef enum ckl_algo {
     CKL_ALGO_UMMA_2CTA = 4,  /* CTA-pair tcgen05.mma (cta_group::2), 256x256 tile per pair */
     CKL_ALGO_UMMA_2CTA_SK = 5,
     CKL_ALGO_UMMA_2CTA_WIDE = 6, /* CTA pair, 256x512 tile filling all of tensor memory */
-    CKL_ALGO_UMMA_2CTA_WIDE_SK = 7
+    CKL_ALGO_UMMA_2CTA_WIDE_SK = 7,
+    CKL_ALGO_UMMA_1CTA_N128 = 8, /* the single-CTA kernel on 128x128 tiles: twice the tiles for
+                                    problems too small to fill the SMs with 128x256 ones */
+    CKL_ALGO_UMMA_1CTA_N128_SK = 9
 } ckl_algo;
 
 /* Stream handle: a cudaStream_t passed as an opaque pointer so this header

@@ -108,8 +108,9 @@ def test_dispatch_follows_the_reference_contract(ckl):
     # (include/ckl/detail/wmma_gemm.cuh:148-158); legal ones to the tensor-core kernel.
     assert ckl.plan_gemm(129, 257, 193).algo == ckl.ALGO_SIMT      # lda=193, ldb=257
     assert ckl.plan_gemm(7, 5, 11).algo == ckl.ALGO_SIMT
-    assert ckl.plan_gemm(256, 256, 256).algo == ckl.ALGO_UMMA_1CTA
-    assert ckl.plan_gemm(512, 384, 640).algo == ckl.ALGO_UMMA_1CTA
+    assert ckl.plan_gemm(256, 256, 256).algo == ckl.ALGO_UMMA_1CTA_N128    # small: 128x128 tiles
+    assert ckl.plan_gemm(512, 384, 640).algo == ckl.ALGO_UMMA_1CTA_N128
+    assert ckl.plan_gemm(2048, 2048, 2048).algo == ckl.ALGO_UMMA_1CTA
     assert ckl.plan_gemm(256, 256, 256, a_align=2).algo == ckl.ALGO_SIMT
     with pytest.raises(ckl.CklError) as e:
         ckl.plan_gemm(129, 257, 193, algo=ckl.ALGO_UMMA_1CTA)
@@ -131,9 +132,10 @@ def test_dispatch_follows_the_reference_contract(ckl):
     assert p.algo == ckl.ALGO_UMMA_2CTA_SK and p.sk_tiles == 16 and p.workspace_bytes > 0
     assert p.units == 64 and p.dp_tiles == 0
     assert [ckl.plan_sk_range(p, u)[0] % p.k_blocks for u in range(8)] == [0, 64, 128, 192] * 2
-    # with a short k per unit the single-CTA tiles keep the job (32 tiles x 4 CTAs)
+    # with a short k per unit the single-CTA kernel keeps the job, on 128x128 tiles because
+    # 128x256 ones would fill at most half of the SMs (64 tiles x 2 CTAs)
     p = ckl.plan_gemm(1024, 1024, 8192)
-    assert p.algo == ckl.ALGO_UMMA_SK and p.units == 128
+    assert p.algo == ckl.ALGO_UMMA_1CTA_N128_SK and p.units == 128 and p.tile_n == 128
     # a last wave that is at most 60 % full is split too, behind whole tiles (44 tiles left for
     # 74 pairs), but only from k = 4096 on: below that the parked partials cost more than the
     # idle SMs; a remainder too thin to give every pair 2048 k of split work takes a whole
@@ -155,6 +157,12 @@ def test_dispatch_follows_the_reference_contract(ckl):
     assert ckl.plan_gemm(2048, 2816, 2048).sk_tiles == 0
     # fewer tiles than units: cut every tile only when the cut saves more than the fix-up pass costs
     assert ckl.plan_gemm(1536, 1536, 1536).sk_tiles == 0
+    # whole 128x256 tiles that would fill at most half of the SMs become 128x128 ones
+    p = ckl.plan_gemm(1536, 1536, 1536)
+    assert p.algo == ckl.ALGO_UMMA_1CTA_N128 and (p.tile_m, p.tile_n, p.tiles_m * p.tiles_n) == (128, 128, 144)
+    assert ckl.plan_gemm(1024, 1024, 1024).algo == ckl.ALGO_UMMA_1CTA_N128
+    assert ckl.plan_gemm(2048, 2048, 2048).algo == ckl.ALGO_UMMA_1CTA          # 128 tiles: enough
+    assert ckl.plan_gemm(512, 128, 512).algo == ckl.ALGO_UMMA_1CTA             # one tile column either way
     p = ckl.plan_gemm(256, 8192, 8192)
     assert p.sk_tiles == 32 and p.units == 64
     # from k = 4096 on the 256x512 tile takes over where its waves fill as well
@@ -206,7 +214,8 @@ SHAPES = [(128, 256, 64), (256, 256, 256), (4000, 3000, 5000), (1024, 1024, 3276
           (8192, 8192, 8192), (8192, 1024, 8192), (16384, 1792, 4096), (200, 264, 72),
           (2304, 4096, 1024), (1000, 776, 520), (128, 256, 6400), (100000, 256, 64)]
 ALGOS = ["ALGO_UMMA_1CTA", "ALGO_UMMA_SK", "ALGO_UMMA_2CTA", "ALGO_UMMA_2CTA_SK",
-         "ALGO_UMMA_2CTA_WIDE", "ALGO_UMMA_2CTA_WIDE_SK"]
+         "ALGO_UMMA_2CTA_WIDE", "ALGO_UMMA_2CTA_WIDE_SK", "ALGO_UMMA_1CTA_N128",
+         "ALGO_UMMA_1CTA_N128_SK"]
 
 
 @pytest.mark.parametrize("sm_count", [148, 132, 8])
@@ -220,7 +229,7 @@ def test_schedule_covers_every_k_block_once(ckl, shape, algo_name, sm_count):
     assert plan.k_blocks == -(-k // plan.tile_k)
     assert plan.dp_tiles + plan.sk_tiles == tiles
     pair = plan.tile_m == 256
-    assert plan.tile_n == (512 if "WIDE" in algo_name else 256)
+    assert plan.tile_n == (512 if "WIDE" in algo_name else 128 if "N128" in algo_name else 256)
     assert plan.grid == plan.units * (2 if pair else 1)
     assert plan.units <= (sm_count // 2 if pair else sm_count)
 
@@ -241,7 +250,7 @@ def test_schedule_covers_every_k_block_once(ckl, shape, algo_name, sm_count):
             assert (slot == -1) == whole
             if slot >= 0:
                 assert slot // 2 == u and slot not in slots_used
-                assert slot * plan.tile_m * plan.tile_n * 4 < plan.workspace_bytes
+                assert slot * plan.tile_m * max(plan.tile_n, 256) * 4 < plan.workspace_bytes
                 slots_used.add(slot)
                 partial_positions.append(idx)
             covered.setdefault(tile, []).append((kb0, kb1, u, slot))

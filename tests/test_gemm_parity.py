@@ -168,7 +168,8 @@ def test_beta_zero_does_not_read_c(env):
 # ---------------------------------------------------------------------------------------
 
 ALGO_NAMES = ["ALGO_SIMT", "ALGO_UMMA_1CTA", "ALGO_UMMA_SK", "ALGO_UMMA_2CTA", "ALGO_UMMA_2CTA_SK",
-              "ALGO_UMMA_2CTA_WIDE", "ALGO_UMMA_2CTA_WIDE_SK"]
+              "ALGO_UMMA_2CTA_WIDE", "ALGO_UMMA_2CTA_WIDE_SK", "ALGO_UMMA_1CTA_N128",
+              "ALGO_UMMA_1CTA_N128_SK"]
 RAGGED = [(128, 256, 64), (200, 264, 72), (1000, 776, 520), (130, 8, 8), (1, 2048, 4096),
           (513, 1032, 1000), (2304, 1280, 2048)]
 
