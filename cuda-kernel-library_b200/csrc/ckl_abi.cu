@@ -360,7 +360,9 @@ Schedule make_schedule(int m, int n, int k, int mode, int max_units, int want_sk
             // against 530 unsplit; 1024 x 1024 x 8192, f = 4, 128 k blocks: 676 against 409).
             const long long f = max_units / tiles;
             const long long saved = f >= 2 ? static_cast<long long>(s.k_blocks) * (f - 1) / f : 0;
-            const long long pass_cost = d.tile_k >= 128 ? 20 : 40;
+            // ... plus a tenth of that per partial tile it adds (512 x 512 x 4096 in 128x128
+            // tiles, f = 9: 113 TFLOP/s cut against 133 uncut).
+            const long long pass_cost = (d.tile_k >= 128 ? 20 : 40) + (d.tile_k >= 128 ? 2 : 4) * f;
             if (tiles * 4 > max_units * 3 || saved < pass_cost) {
                 return s;
             }
