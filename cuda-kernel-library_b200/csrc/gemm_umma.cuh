@@ -8,10 +8,12 @@
 // src/gemm/gemm_mma_opt.cu:87-195).  It shares nothing with them: there is no
 // mma.sync, ldmatrix or cp.async here.
 //
-// One kernel template, two shapes of worker ("unit"):
+// One kernel template, three shapes of worker ("unit"; KernelMode below):
 //
 //   kPair = false   one CTA per unit, output tile 128 x 256, UMMA 128x256x16,
-//                   4-stage ring of (A 128x64, B 64x256) = 48 KB per stage.
+//                   4-stage ring of (A 128x64, B 64x256) = 48 KB per stage.  With
+//                   GemmParams::tile_n = 128 the same kernel runs 128 x 128 tiles
+//                   (half of the B boxes, UMMA 128x128x16) for small problems.
 //   kPair = true    a cluster of two CTAs per unit, output tile 256 x 256,
 //                   UMMA 256x256x16 issued by the leader CTA for both SMs
 //                   (cta_group::2).  Each CTA loads only its own 128 rows of A
