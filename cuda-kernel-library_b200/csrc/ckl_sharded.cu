@@ -322,6 +322,9 @@ int ckl_plan_host_sharded(int m, int world, int rank, ckl_host_shard_plan* out) 
     // one GEMM over world * panel_rows rows; finer panels shorten the tail of the pipeline
     // but cost launches and make the GEMMs small.
     int panels = std::max(1, std::min(4, rpr / 128));
+    if (const char* forced = std::getenv("CKL_HOST_PANELS")) {  // tuning knob: 1..8, the same on every rank
+        panels = std::max(1, std::min(kMaxPanels, std::atoi(forced)));
+    }
     int panel_rows = (rpr + panels - 1) / panels;
     panel_rows = (panel_rows + 7) / 8 * 8;
     panels = rpr > 0 ? (rpr + panel_rows - 1) / panel_rows : 0;
