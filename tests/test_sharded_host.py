@@ -197,3 +197,25 @@ def test_gather_refuses_uneven_shards():
                         assemble=lambda *a: None)
     with pytest.raises(ValueError):
         op.gather(torch.zeros(8, op.shard.width), None, None)
+
+
+def test_communicator_validates_before_it_touches_a_device(ckl):
+    """Bad arguments are refused by the C ABI without a GPU; a well-formed request on a machine
+    without one fails with a CUDA error instead of pretending."""
+    with pytest.raises(ckl.CklError) as e:
+        ckl.Comm(0, 0, None)
+    assert e.value.status == ckl.ERR_INVALID_ARG
+    with pytest.raises(ckl.CklError) as e:
+        ckl.Comm(2, 2, bytes(ckl.COMM_ID_BYTES))
+    assert e.value.status == ckl.ERR_INVALID_ARG
+    with pytest.raises(ckl.CklError) as e:
+        ckl.Comm(2, 0, None)                      # several ranks need the shared id
+    assert e.value.status == ckl.ERR_INVALID_ARG
+    with pytest.raises(ValueError):
+        ckl.Comm(2, 0, b"short")
+    if not torch.cuda.is_available():
+        with pytest.raises(ckl.CklError) as e:
+            ckl.Comm(1, 0, None)
+        assert e.value.status in (ckl.ERR_CUDA, ckl.ERR_UNSUPPORTED)
+        with pytest.raises(ckl.CklError):
+            ckl.scatter_column_block([1 << 20], 1 << 21, 2, 4, 8, 8, 4)   # col0 + width > n
