@@ -292,3 +292,41 @@ def test_raster_groups_keep_a_wave_compact(ckl):
     cols = {s[2] for s in first_wave}
     # 148 tiles in flight touch 16 tile rows and 10 tile columns, not a 1 x 148 strip
     assert len(rows) == plan.group_m == 16 and len(cols) <= 10
+
+
+def test_cpp_headers_compile_and_link_against_the_library(tmp_path):
+    """include/ckl/gemm.hpp (the reference's names as inline shims plus the additions: 16-bit C,
+    leading dimensions, the N-sharded wrappers) and include/ckl/trsm.hpp compile as C++17 and
+    link against libckl_gemm.so; a program that only takes addresses runs without a GPU."""
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc not available")
+    src = tmp_path / "use_headers.cu"
+    src.write_text(r'''
+#include <cstdio>
+#include "ckl/gemm.hpp"
+#include "ckl/trsm.hpp"
+int main() {
+    // instantiate every wrapper; none is called (no GPU needed)
+    void (*f16)(const __half*, const __half*, float*, int, int, int, float, float, cudaStream_t) = ckl::gemm_mma_opt;
+    void (*bf16)(const __nv_bfloat16*, const __nv_bfloat16*, float*, int, int, int, float, float, cudaStream_t) = ckl::gemm_wmma_bf16;
+    void (*tensor)(const __nv_bfloat16*, const __nv_bfloat16*, __nv_bfloat16*, int, int, int, int, int, int, float, float,
+                   cudaStream_t, int) = ckl::gemm_tensor<__nv_bfloat16, __nv_bfloat16>;
+    auto host = &ckl::gemm_tensor_host_sharded<__nv_bfloat16, __nv_bfloat16>;
+    auto gathered = &ckl::gemm_tensor_gathered<__half, float>;
+    int col0 = -1, width = -1;
+    const int rc = ckl_column_shard(14336, 8, 3, 8, &col0, &width);
+    std::printf("%d %d %d %d\n", rc, col0, width, (f16 && bf16 && tensor && host && gathered) ? 1 : 0);
+    return 0;
+}
+''')
+    exe = tmp_path / "use_headers"
+    pkg = os.path.join(ROOT, "cuda-kernel-library_b200")
+    out = subprocess.run([nvcc, "-std=c++17", "-Wno-deprecated-gpu-targets", "-I", os.path.join(ROOT, "include"),
+                          "-o", str(exe), str(src), "-L", pkg, "-lckl_gemm", "-Xlinker", "-rpath", "-Xlinker", pkg],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-3000:]
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=60)
+    assert run.returncode == 0 and run.stdout.split() == ["0", "5376", "1792", "1"], run.stdout + run.stderr
