@@ -84,7 +84,7 @@ def test_host_shard_plan_deals_every_row_once(ckl):
         rows = _device_rows(lambda r: plans[r], world)
         assert sorted(rows[rows >= 0].tolist()) == list(range(m))
     assert ckl.plan_host_sharded(8192, 8, 3).rows == 1024
-    assert ckl.plan_host_sharded(8192, 8, 3).panels == 4
+    assert ckl.plan_host_sharded(8192, 8, 3).panels == 8 and ckl.plan_host_sharded(8192, 8, 3).panel_rows == 128
     with pytest.raises(ckl.CklError):
         ckl.plan_host_sharded(8, 2, 2)
 
