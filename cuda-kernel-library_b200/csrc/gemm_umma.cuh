@@ -517,7 +517,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     // ---- roles ----------------------------------------------------------------
     if (warp == 0) {
-        if (lane == 0) {
+        if (ptx::elect_one_sync()) {
             // TMA producer.
             SegmentCursor cur = make_cursor(sched, unit);
             Segment seg;
@@ -639,7 +639,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && leader) {
+        if (leader && ptx::elect_one_sync()) {
             // MMA issuer.
             SegmentCursor cur = make_cursor(sched, unit);
             Segment seg;
