@@ -109,12 +109,15 @@ sgemm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c,
         }
     };
 
-    float acc[kR][kR];
+    // Accumulators as column pairs: the packed FP32 multiply-add of sm_100 (two independent
+    // IEEE round-to-nearest FMAs per instruction, bit-identical to fmaf on each half) takes half
+    // the issue slots of scalar FMAs, which is what this kernel was short of.
+    float2 acc[kR][kR / 2];
 #pragma unroll
     for (int i = 0; i < kR; ++i) {
 #pragma unroll
-        for (int j = 0; j < kR; ++j) {
-            acc[i][j] = 0.0f;
+        for (int j = 0; j < kR / 2; ++j) {
+            acc[i][j] = make_float2(0.0f, 0.0f);
         }
     }
 
@@ -131,19 +134,22 @@ sgemm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c,
         }
 #pragma unroll
         for (int kk = 0; kk < kTileK; ++kk) {
-            float av[kR], bv[kR];
+            float av[kR];
+            float2 bv[kR / 2];
 #pragma unroll
             for (int h = 0; h < kR / 4; ++h) {
                 const float4 av4 = *reinterpret_cast<const float4*>(&sa[cur][kk][h * 64 + ty * 4]);
                 const float4 bv4 = *reinterpret_cast<const float4*>(&sb[cur][kk][h * 64 + tx * 4]);
                 av[h * 4 + 0] = av4.x; av[h * 4 + 1] = av4.y; av[h * 4 + 2] = av4.z; av[h * 4 + 3] = av4.w;
-                bv[h * 4 + 0] = bv4.x; bv[h * 4 + 1] = bv4.y; bv[h * 4 + 2] = bv4.z; bv[h * 4 + 3] = bv4.w;
+                bv[h * 2 + 0] = make_float2(bv4.x, bv4.y);
+                bv[h * 2 + 1] = make_float2(bv4.z, bv4.w);
             }
 #pragma unroll
             for (int i = 0; i < kR; ++i) {
+                const float2 a2 = make_float2(av[i], av[i]);
 #pragma unroll
-                for (int j = 0; j < kR; ++j) {
-                    acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+                for (int j = 0; j < kR / 2; ++j) {
+                    acc[i][j] = __ffma2_rn(a2, bv[j], acc[i][j]);
                 }
             }
         }
@@ -169,22 +175,23 @@ sgemm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c,
                 float4 out;
                 if (beta != 0.0f) {
                     const float4 old = *reinterpret_cast<const float4*>(dst);
-                    out.x = fmaf(beta, old.x, alpha * acc[i][h * 4 + 0]);
-                    out.y = fmaf(beta, old.y, alpha * acc[i][h * 4 + 1]);
-                    out.z = fmaf(beta, old.z, alpha * acc[i][h * 4 + 2]);
-                    out.w = fmaf(beta, old.w, alpha * acc[i][h * 4 + 3]);
+                    out.x = fmaf(beta, old.x, alpha * acc[i][h * 2 + 0].x);
+                    out.y = fmaf(beta, old.y, alpha * acc[i][h * 2 + 0].y);
+                    out.z = fmaf(beta, old.z, alpha * acc[i][h * 2 + 1].x);
+                    out.w = fmaf(beta, old.w, alpha * acc[i][h * 2 + 1].y);
                 } else {
-                    out.x = alpha * acc[i][h * 4 + 0];
-                    out.y = alpha * acc[i][h * 4 + 1];
-                    out.z = alpha * acc[i][h * 4 + 2];
-                    out.w = alpha * acc[i][h * 4 + 3];
+                    out.x = alpha * acc[i][h * 2 + 0].x;
+                    out.y = alpha * acc[i][h * 2 + 0].y;
+                    out.z = alpha * acc[i][h * 2 + 1].x;
+                    out.w = alpha * acc[i][h * 2 + 1].y;
                 }
                 *reinterpret_cast<float4*>(dst) = out;
             } else {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     if (col + e < n) {
-                        const float v = alpha * acc[i][h * 4 + e];
+                        const float2 pair = acc[i][h * 2 + (e >> 1)];
+                        const float v = alpha * ((e & 1) ? pair.y : pair.x);
                         dst[e] = beta != 0.0f ? fmaf(beta, dst[e], v) : v;
                     }
                 }
