@@ -10,8 +10,8 @@
 // four 4 x 4 blocks (rows ty*4 and 64+ty*4, columns tx*4 and 64+tx*4, so every shared-memory
 // read is a conflict-free or broadcast 16-byte load).  A 64 x 64 tile (one 4 x 4 block per
 // thread) takes the problems that would leave most SMs without a 128 x 128 tile.  The next
-// slab travels global memory -> registers while the current one is multiplied, then
-// registers -> the other shared buffer: one __syncthreads per slab.  A is stored transposed
+// slab travels while the current one is multiplied (A through registers, B with asynchronous
+// copies when the operands are aligned) into the other shared buffer: one __syncthreads per slab.  A is stored transposed
 // (sa[k][row]) so that the inner loop reads four consecutive rows with one load.
 #pragma once
 
@@ -51,9 +51,14 @@ sgemm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c,
     const int m0 = static_cast<int>(blockIdx.y) * kTileM;
     const int n0 = static_cast<int>(blockIdx.x) * kTileN;
 
-    // Global -> register staging of one slab: kLoads float4 of A and of B per thread.
-    float4 ra[kLoads], rb[kLoads];
-    auto fetch = [&](int k0) {
+    // Staging of one slab.  A travels global memory -> registers -> shared memory, because it
+    // is stored transposed.  B keeps its layout, so with aligned operands (kVec) it goes
+    // straight into the other shared buffer with 16-byte asynchronous copies (zero-filled past
+    // the edges of the matrix), which frees eight staging registers; otherwise through
+    // registers like A.
+    float4 ra[kLoads];
+    float4 rb[kVec ? 1 : kLoads];
+    auto fetch = [&](int k0, int buf) {
 #pragma unroll
         for (int i = 0; i < kLoads; ++i) {
             const int idx = tid + i * kThreads;
@@ -79,19 +84,25 @@ sgemm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c,
                 // B: 16 k x kTile columns, four consecutive columns of one k row
                 const int kr = k0 + idx / kBRowQuads;
                 const int col = n0 + (idx % kBRowQuads) * 4;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (kr < k) {
-                    const float* src = b + static_cast<size_t>(kr) * ldb + col;
-                    if (kVec && col + 3 < n) {
-                        v = *reinterpret_cast<const float4*>(src);
-                    } else {
+                if constexpr (kVec) {
+                    const bool inside = kr < k && col < n;
+                    const int bytes = inside ? min(16, (n - col) * 4) : 0;
+                    const float* src = inside ? b + static_cast<size_t>(kr) * ldb + col : b;
+                    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(
+                        &sb[buf][idx / kBRowQuads][(idx % kBRowQuads) * 4]));
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes)
+                                 : "memory");
+                } else {
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (kr < k) {
+                        const float* src = b + static_cast<size_t>(kr) * ldb + col;
                         if (col < n) v.x = src[0];
                         if (col + 1 < n) v.y = src[1];
                         if (col + 2 < n) v.z = src[2];
                         if (col + 3 < n) v.w = src[3];
                     }
+                    rb[i] = v;
                 }
-                rb[i] = v;
             }
         }
     };
@@ -105,7 +116,12 @@ sgemm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c,
             sa[buf][kq + 1][r] = ra[i].y;
             sa[buf][kq + 2][r] = ra[i].z;
             sa[buf][kq + 3][r] = ra[i].w;
-            *reinterpret_cast<float4*>(&sb[buf][idx / kBRowQuads][(idx % kBRowQuads) * 4]) = rb[i];
+            if constexpr (!kVec) {
+                *reinterpret_cast<float4*>(&sb[buf][idx / kBRowQuads][(idx % kBRowQuads) * 4]) = rb[i];
+            }
+        }
+        if constexpr (kVec) {
+            asm volatile("cp.async.wait_all;" ::: "memory");
         }
     };
 
@@ -123,14 +139,14 @@ sgemm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c,
 
     const int slabs = (k + kTileK - 1) / kTileK;
     if (slabs > 0) {
-        fetch(0);
+        fetch(0, 0);
         stash(0);
     }
     __syncthreads();
     for (int s = 0; s < slabs; ++s) {
         const int cur = s & 1;
         if (s + 1 < slabs) {
-            fetch((s + 1) * kTileK);
+            fetch((s + 1) * kTileK, cur ^ 1);  // that buffer was last read one slab ago
         }
 #pragma unroll
         for (int kk = 0; kk < kTileK; ++kk) {
