@@ -11,7 +11,7 @@
 // read is a conflict-free or broadcast 16-byte load).  A 64 x 64 tile (one 4 x 4 block per
 // thread) takes the problems that would leave most SMs without a 128 x 128 tile.  The next
 // slab travels while the current one is multiplied (A through registers, B with asynchronous
-// copies when the operands are aligned) into the other shared buffer: one __syncthreads per slab.  A is stored transposed
+// copies in the large tile when the operands are aligned) into the other shared buffer: one __syncthreads per slab.  A is stored transposed
 // (sa[k][row]) so that the inner loop reads four consecutive rows with one load.
 #pragma once
 
@@ -52,12 +52,14 @@ sgemm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c,
     const int n0 = static_cast<int>(blockIdx.x) * kTileN;
 
     // Staging of one slab.  A travels global memory -> registers -> shared memory, because it
-    // is stored transposed.  B keeps its layout, so with aligned operands (kVec) it goes
-    // straight into the other shared buffer with 16-byte asynchronous copies (zero-filled past
-    // the edges of the matrix), which frees eight staging registers; otherwise through
-    // registers like A.
+    // is stored transposed.  B keeps its layout, so in the large tile with aligned operands it
+    // goes straight into the other shared buffer with 16-byte asynchronous copies (zero-filled
+    // past the edges of the matrix), which frees eight staging registers; otherwise through
+    // registers like A (the small tile is faster that way: its problems are short and
+    // latency-bound).
+    constexpr bool kAsyncB = kVec && kTile == 128;
     float4 ra[kLoads];
-    float4 rb[kVec ? 1 : kLoads];
+    float4 rb[kAsyncB ? 1 : kLoads];
     auto fetch = [&](int k0, int buf) {
 #pragma unroll
         for (int i = 0; i < kLoads; ++i) {
@@ -84,7 +86,7 @@ sgemm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c,
                 // B: 16 k x kTile columns, four consecutive columns of one k row
                 const int kr = k0 + idx / kBRowQuads;
                 const int col = n0 + (idx % kBRowQuads) * 4;
-                if constexpr (kVec) {
+                if constexpr (kAsyncB) {
                     const bool inside = kr < k && col < n;
                     const int bytes = inside ? min(16, (n - col) * 4) : 0;
                     const float* src = inside ? b + static_cast<size_t>(kr) * ldb + col : b;
@@ -96,10 +98,14 @@ sgemm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c,
                     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (kr < k) {
                         const float* src = b + static_cast<size_t>(kr) * ldb + col;
-                        if (col < n) v.x = src[0];
-                        if (col + 1 < n) v.y = src[1];
-                        if (col + 2 < n) v.z = src[2];
-                        if (col + 3 < n) v.w = src[3];
+                        if (kVec && col + 3 < n) {
+                            v = *reinterpret_cast<const float4*>(src);
+                        } else {
+                            if (col < n) v.x = src[0];
+                            if (col + 1 < n) v.y = src[1];
+                            if (col + 2 < n) v.z = src[2];
+                            if (col + 3 < n) v.w = src[3];
+                        }
                     }
                     rb[i] = v;
                 }
@@ -116,11 +122,11 @@ sgemm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* c,
             sa[buf][kq + 1][r] = ra[i].y;
             sa[buf][kq + 2][r] = ra[i].z;
             sa[buf][kq + 3][r] = ra[i].w;
-            if constexpr (!kVec) {
+            if constexpr (!kAsyncB) {
                 *reinterpret_cast<float4*>(&sb[buf][idx / kBRowQuads][(idx % kBRowQuads) * 4]) = rb[i];
             }
         }
-        if constexpr (kVec) {
+        if constexpr (kAsyncB) {
             asm volatile("cp.async.wait_all;" ::: "memory");
         }
     };
