@@ -100,6 +100,31 @@ def test_leading_dimensions_and_alignment(ckl, orc, offset):
     assert (host[:, n:] == 7.0).all()      # padding columns untouched
 
 
+@pytest.mark.parametrize("offset", [0, 1], ids=["aligned", "misaligned"])
+def test_large_tile_with_ragged_edges_inside_padded_buffers(ckl, orc, offset):
+    """Enough 128 x 128 tiles for the large-tile kernel, with n and k that end inside a group of
+    four and leading dimensions that keep 16-byte alignment: the aligned case stages B with
+    partial asynchronous copies at the right edge and whole zero-filled ones past k."""
+    m, n, k = 2000, 1290, 333
+    lda, ldb, ldc = 336, 1292, 1296
+    a, b, c0 = _inputs(orc, m, n, k)
+    big_a = torch.zeros(m * lda + offset, dtype=torch.float32, device="cuda")
+    big_b = torch.full((k * ldb + offset,), float("nan"), dtype=torch.float32, device="cuda")
+    big_c = torch.full((m * ldc + offset,), 7.0, dtype=torch.float32, device="cuda")
+    va = big_a[offset:].view(m, lda)
+    vb = big_b[offset:].view(k, ldb)
+    vc = big_c[offset:].view(m, ldc)
+    va[:, :k] = _dev(a, m, k)
+    vb[:, :n] = _dev(b, k, n)          # the padding columns of B stay NaN: they must not be used
+    vc[:, :n] = _dev(c0, m, n)
+    ckl.sgemm(va.data_ptr(), vb.data_ptr(), vc.data_ptr(), m, n, k, lda, ldb, ldc, 0.5, -1.0)
+    torch.cuda.synchronize()
+    host = vc.cpu().numpy()
+    ref, _ = orc.gemm_reference_mt(a, b, c0, 0.5, -1.0)
+    assert orc.relative_frobenius_error(np.ascontiguousarray(host[:, :n]), ref) < 5e-6
+    assert (host[:, n:] == 7.0).all()      # padding columns untouched
+
+
 def test_larger_square_matches_sampled_oracle(ckl, orc):
     """2048^3: full rows and columns of the exact oracle (the whole matrix would take minutes)."""
     m = n = k = 2048
